@@ -1,0 +1,532 @@
+// Forward pass of block-diffusion attention for sm_100a.
+//
+// Replaces the reference's forward stack (csrc/fda/flash_fwd_kernel_sm90.h:165-325,
+// csrc/fda/mainloop_fwd_sm90_tma_gmma_ws.hpp:334-880, csrc/fda/epilogue_fwd.hpp:126-272,
+// csrc/fda/softmax.h:92-168 and the forward scheduler csrc/fda/tile_scheduler.hpp:51-185) with a design
+// built around tcgen05:
+//
+//   * a work item is kQTiles consecutive 128-row query tiles of one half of one (sample, head); both tiles
+//     walk ONE list of 128-key tiles (clean prefix, then the noisy diagonal), so a K/V tile fetched once by TMA
+//     feeds both; a tile that one of the query tiles cannot see is skipped for that query tile only;
+//   * warp roles: kQTiles softmax warpgroups (thread = one query row), one TMA producer warp, one MMA warp;
+//   * S = Q K^T and O += P V are tcgen05.mma with fp32 accumulators in tensor memory; P is written back over
+//     S as 16-bit and consumed from tensor memory as the A operand; V is used MN-major straight from its TMA
+//     layout;
+//   * online softmax with the scale folded into one FMA + exp2, a running row maximum that is only advanced
+//     when it grows by more than 2^8 (O is rescaled in tensor memory only then), LSE in natural-log units;
+//   * only visible tiles are enumerated, only tiles crossing a block boundary (or the end of a half) get the
+//     element mask;
+//   * persistent CTAs; items are ordered longest first (query tiles near the end of a half see most keys).
+//
+// Numerics contract kept from the reference: fp32 accumulation, softcap applied before the mask
+// (mainloop_fwd...hpp:679-683), P rounded to the input dtype before P V (:782), row sums accumulated in fp32
+// from the unrounded P, LSE = max * scale + ln(sum) (softmax.h:137-154).
+#include "geometry.h"
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace fda {
+namespace {
+
+constexpr int kBlockM = 128;  // query rows per tile (= tensor-memory lanes)
+constexpr int kBlockN = 128;  // keys per tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+
+struct FwdParams {
+  CUtensorMap tm_q, tm_k, tm_v;
+  void* out;
+  float* lse;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  const int32_t* cu_seqlens;
+  int batch, seqlen, total, heads, heads_k, head_dim, block_size;
+  int items_per_half;  // ceil(max n / rows per item)
+  int total_items;
+  float scale_log2;    // exponent scale: softmax_scale*log2(e), or softcap*log2(e) with softcapping
+  float softcap_pre;   // softmax_scale / softcap (tanh argument scale)
+  float lse_scale;     // natural-log scale of the row maximum: softmax_scale, or softcap
+};
+
+struct Item {
+  int b, h, hk, qh, qa, qb, n;
+  int row0;    // tensor row of the first token of the sample
+  int bcoord;  // batch coordinate for TMA (0 when packed)
+  bool valid;
+};
+
+template <int kQTiles>
+__device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
+  Item it;
+  const int per_p = 2 * p.heads * p.batch;
+  const int p_rev = idx / per_p;
+  const int rem = idx - p_rev * per_p;
+  it.qh = rem & 1;
+  const int bh = rem >> 1;
+  it.b = bh / p.heads;
+  it.h = bh - it.b * p.heads;
+  it.hk = it.h / (p.heads / p.heads_k);
+  const int pidx = p.items_per_half - 1 - p_rev;
+  if (p.cu_seqlens != nullptr) {
+    const int s = p.cu_seqlens[it.b];
+    const int e = p.cu_seqlens[it.b + 1];
+    it.n = (e - s) / 2;
+    it.row0 = s;
+    it.bcoord = 0;
+  } else {
+    it.n = p.seqlen / 2;
+    it.row0 = 0;
+    it.bcoord = it.b;
+  }
+  it.qa = pidx * kQTiles * kBlockM;
+  it.valid = it.qa < it.n;
+  it.qb = imin(it.qa + kQTiles * kBlockM, it.n);
+  return it;
+}
+
+// Classification of key tile (kh, kt) for query tile t of the item (skip when the tile has no rows).
+template <int kQTiles>
+__device__ __forceinline__ int classify_for(const Item& it, int t, int kh, int kt, int bs) {
+  const int ta = it.qa + t * kBlockM;
+  if (ta >= it.qb) return kTileSkip;
+  const int tb = imin(ta + kBlockM, it.qb);
+  return classify_tile(it.qh, kh, ta, tb, kt * kBlockN, kBlockN, it.n, bs);
+}
+
+template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+struct FwdConfig {
+  static constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // one 128-row tile of Q, K or V
+  static constexpr int kPanels = kHeadDim / 64;              // 64-column panels (128-byte rows)
+  static constexpr int kPanelBytes = 128 * 128;
+  static constexpr int kThreads = 128 * kQTiles + 64;
+  static constexpr int kLoadWarp = 4 * kQTiles;
+  static constexpr int kMmaWarp = 4 * kQTiles + 1;
+  static constexpr int kSmemBytes = (kQTiles + kStages) * kTileBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr int kTmemS = 0;                  // S_t at t*128
+  static constexpr int kTmemO = 128 * kQTiles;      // O_t at kTmemO + t*kHeadDim
+  static_assert(kTmemO + kQTiles * kHeadDim <= 512, "tensor memory budget");
+};
+
+template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+__global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + kQTiles * Cfg::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * Cfg::kTileBytes);
+  uint64_t* q_full = bars;                       // 1
+  uint64_t* q_empty = bars + 1;                  // 1
+  uint64_t* kv_full = bars + 2;                  // kStages
+  uint64_t* kv_empty = kv_full + kStages;        // kStages
+  uint64_t* s_full = kv_empty + kStages;         // kQTiles
+  uint64_t* p_full = s_full + kQTiles;           // kQTiles
+  uint64_t* o_full = p_full + kQTiles;           // kQTiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kQTiles);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_empty, 1);
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&kv_full[i], 1);
+      ptx::mbar_init(&kv_empty[i], 1);
+    }
+    for (int t = 0; t < kQTiles; ++t) {
+      ptx::mbar_init(&s_full[t], 1);
+      ptx::mbar_init(&p_full[t], 128);
+      ptx::mbar_init(&o_full[t], 1);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == Cfg::kLoadWarp) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&p.tm_q);
+      ptx::prefetch_tensormap(&p.tm_k);
+      ptx::prefetch_tensormap(&p.tm_v);
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int bs = p.block_size;
+
+  if (warp == Cfg::kLoadWarp) {
+    // ------------------------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t slot = 0, n_item = 0;
+      bool alive = true;
+      for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+        const Item it = decode_item<kQTiles>(p, idx);
+        if (!it.valid) continue;
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
+        const int steps = plan.steps();
+        const int q_row = it.row0 + it.qh * it.n + it.qa;
+        const int ntiles = ceil_div(it.qb - it.qa, kBlockM);
+        for (int s = 0; s < steps && alive; ++s) {
+          int kh, kt;
+          plan.step(s, kh, kt);
+          const int k_row = it.row0 + kh * it.n + kt * kBlockN;
+          for (int which = 0; which < 2; ++which) {  // 0: K tile, 1: V tile
+            const uint32_t stage = slot % kStages;
+            if (!ptx::mbar_wait(&kv_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 11)) { alive = false; break; }
+            ptx::mbar_expect_tx(&kv_full[stage], Cfg::kTileBytes);
+            uint8_t* dst = sKV + stage * Cfg::kTileBytes;
+            const CUtensorMap* tm = which == 0 ? &p.tm_k : &p.tm_v;
+#pragma unroll
+            for (int c = 0; c < Cfg::kPanels; ++c) {
+              ptx::tma_load_4d(dst + c * Cfg::kPanelBytes, tm, &kv_full[stage], c * 64, k_row, it.hk, it.bcoord);
+            }
+            ++slot;
+            if (s == 0 && which == 0) {
+              // Q after the first K tile: the first MMA needs both, the previous item may still own Q.
+              if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 12)) { alive = false; break; }
+              ptx::mbar_expect_tx(q_full, ntiles * Cfg::kTileBytes);
+              for (int t = 0; t < ntiles; ++t) {
+#pragma unroll
+                for (int c = 0; c < Cfg::kPanels; ++c) {
+                  ptx::tma_load_4d(sQ + t * Cfg::kTileBytes + c * Cfg::kPanelBytes, &p.tm_q, q_full, c * 64,
+                                   q_row + t * kBlockM, it.h, it.bcoord);
+                }
+              }
+            }
+          }
+        }
+        ++n_item;
+      }
+      if (*abort_flag) __nanosleep(100000);  // let copies in flight land before the CTA exits
+    }
+  } else if (warp == Cfg::kMmaWarp) {
+    // --------------------------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr int kFmt = kBf16 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc(kBlockM, kBlockN, kFmt, false, false);
+      const uint32_t idesc_o = ptx::make_idesc(kBlockM, kHeadDim, kFmt, false, true);
+      uint32_t slot = 0, n_item = 0;
+      uint32_t cnt_p[kQTiles];
+#pragma unroll
+      for (int t = 0; t < kQTiles; ++t) cnt_p[t] = 0;
+      bool alive = true;
+
+      auto issue_s = [&](int t, uint32_t k_stage) {
+        const uint32_t a0 = ptx::smem_u32(sQ + t * Cfg::kTileBytes);
+        const uint32_t b0 = ptx::smem_u32(sKV + k_stage * Cfg::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+          const uint32_t off = (kk / 4) * Cfg::kPanelBytes + (kk % 4) * 32;
+          ptx::umma_ss_f16(tmem + Cfg::kTmemS + t * 128, ptx::make_smem_desc(a0 + off, 16, 1024),
+                           ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+        }
+      };
+      auto issue_pv = [&](int t, uint32_t v_stage, bool accumulate) {
+        const uint32_t b0 = ptx::smem_u32(sKV + v_stage * Cfg::kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBlockN / 16; ++kk) {
+          ptx::umma_ts_f16(tmem + Cfg::kTmemO + t * kHeadDim, tmem + Cfg::kTmemS + t * 128 + kk * 8,
+                           ptx::make_smem_desc(b0 + kk * 2048, Cfg::kPanelBytes, 1024), idesc_o,
+                           (accumulate || kk > 0) ? 1u : 0u);
+        }
+      };
+
+      for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+        const Item it = decode_item<kQTiles>(p, idx);
+        if (!it.valid) continue;
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
+        const int steps = plan.steps();
+        if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 21)) { alive = false; break; }
+        bool pend[kQTiles], o_acc[kQTiles];
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) { pend[t] = false; o_acc[t] = false; }
+        for (int s = 0; s <= steps && alive; ++s) {
+          const uint32_t slot_k = slot + 2 * s;        // K tile of step s
+          const uint32_t slot_v = slot + 2 * s - 1;    // V tile of step s-1
+          int kh = 0, kt = 0;
+          if (s < steps) {
+            plan.step(s, kh, kt);
+            if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 22)) { alive = false; break; }
+          }
+          if (s > 0) {
+            if (!ptx::mbar_wait(&kv_full[slot_v % kStages], (slot_v / kStages) & 1, abort_flag, 23)) { alive = false; break; }
+          }
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int t = 0; t < kQTiles; ++t) {
+            if (pend[t]) {
+              if (!ptx::mbar_wait(&p_full[t], cnt_p[t] & 1, abort_flag, 24)) { alive = false; break; }
+              ++cnt_p[t];
+              ptx::tc_fence_after();
+              issue_pv(t, slot_v % kStages, o_acc[t]);
+              o_acc[t] = true;
+              pend[t] = false;
+            }
+            if (s < steps && classify_for<kQTiles>(it, t, kh, kt, bs) != kTileSkip) {
+              issue_s(t, slot_k % kStages);
+              ptx::umma_commit(&s_full[t]);
+              pend[t] = true;
+            }
+          }
+          if (!alive) break;
+          if (s > 0) ptx::umma_commit(&kv_empty[slot_v % kStages]);
+          if (s < steps) ptx::umma_commit(&kv_empty[slot_k % kStages]);
+        }
+        if (!alive) break;
+        ptx::umma_commit(q_empty);
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) {
+          if (it.qa + t * kBlockM < it.qb) ptx::umma_commit(&o_full[t]);
+        }
+        slot += 2 * steps;
+        ++n_item;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------ softmax + epilogue
+    const int t = warp >> 2;                       // query tile of this warpgroup
+    const int quad = warp & 3;                     // tensor-memory lane quadrant of this warp
+    const int row = quad * 32 + lane;              // row inside the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t tmem_s = tmem + Cfg::kTmemS + t * 128 + lane_addr;
+    const uint32_t tmem_o = tmem + Cfg::kTmemO + t * kHeadDim + lane_addr;
+    uint32_t cnt_s = 0, cnt_o = 0;
+    bool alive = true;
+    for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+      const Item it = decode_item<kQTiles>(p, idx);
+      if (!it.valid) continue;
+      const int ta = it.qa + t * kBlockM;
+      if (ta >= it.qb) continue;
+      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
+      const int steps = plan.steps();
+      const int r = ta + row;                      // position in the half
+      const bool row_valid = r < it.n;
+      const int r_eff = row_valid ? r : it.n - 1;
+      const int blk0 = block_lo(r_eff, bs);
+      const int blk1 = imin(blk0 + bs, it.n);
+      float m_run = -INFINITY;  // reference maximum (unscaled scores, or tanh values with softcap)
+      float l_run = 0.f;
+      bool o_started = false;
+      for (int s = 0; s < steps && alive; ++s) {
+        int kh, kt;
+        plan.step(s, kh, kt);
+        const int cls = classify_for<kQTiles>(it, t, kh, kt, bs);
+        if (cls == kTileSkip) continue;
+        if (!ptx::mbar_wait(&s_full[t], cnt_s & 1, abort_flag, 31)) { alive = false; break; }
+        ++cnt_s;
+        ptx::tc_fence_after();
+        float v[kBlockN];
+        {
+          uint32_t* u = reinterpret_cast<uint32_t*>(v);
+#pragma unroll
+          for (int c = 0; c < kBlockN / 32; ++c) ptx::tmem_ld32(tmem_s + c * 32, u + c * 32);
+          ptx::tmem_wait_ld();
+        }
+        if (kSoftcap) {
+#pragma unroll
+          for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * p.softcap_pre);
+        }
+        if (cls == kTileMasked) {
+          int lo, hi;
+          if (it.qh == 1) { lo = 0; hi = blk1; }
+          else if (kh == 1) { lo = 0; hi = blk0; }
+          else { lo = blk0; hi = blk1; }
+          lo -= kt * kBlockN;
+          hi -= kt * kBlockN;
+#pragma unroll
+          for (int c = 0; c < kBlockN; ++c) {
+            if (c < lo || c >= hi) v[c] = -INFINITY;
+          }
+        }
+        float m_tile = v[0];
+#pragma unroll
+        for (int c = 1; c < kBlockN; ++c) m_tile = fmaxf(m_tile, v[c]);
+        const float m_new = fmaxf(m_run, m_tile);
+        // advance the reference maximum only when it grew by more than the threshold (always on the first tile)
+        const bool need = (m_new - m_run) * p.scale_log2 > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          const float factor = need ? ptx::ex2((m_run - m_new) * p.scale_log2) : 1.f;
+          if (o_started) {
+#pragma unroll
+            for (int c = 0; c < kHeadDim / 32; ++c) {
+              uint32_t o[32];
+              ptx::tmem_ld32(tmem_o + c * 32, o);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              ptx::tmem_st32(tmem_o + c * 32, o);
+            }
+          }
+          l_run *= factor;
+          if (need) m_run = m_new;
+        }
+        const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
+        const float neg_m = -m_ref * p.scale_log2;
+        float sum = 0.f;
+        uint32_t pk[kBlockN / 2];
+#pragma unroll
+        for (int c = 0; c < kBlockN; c += 2) {
+          const float p0 = ptx::ex2(fmaf(v[c], p.scale_log2, neg_m));
+          const float p1 = ptx::ex2(fmaf(v[c + 1], p.scale_log2, neg_m));
+          sum += p0 + p1;
+          pk[c / 2] = ptx::pack2<kBf16>(p0, p1);
+        }
+        l_run += sum;
+#pragma unroll
+        for (int c = 0; c < kBlockN / 64; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(&p_full[t]);
+        o_started = true;
+      }
+      if (!alive) break;
+      // ---- epilogue: O / l -> global, LSE
+      if (!ptx::mbar_wait(&o_full[t], cnt_o & 1, abort_flag, 32)) { alive = false; break; }
+      ++cnt_o;
+      ptx::tc_fence_after();
+      const float inv_l = 1.f / l_run;
+      const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
+      if (kBf16 || !kBf16) {
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + it.bcoord * p.o_batch_stride + srow * p.o_row_stride +
+                         it.h * p.o_head_stride;
+#pragma unroll
+        for (int c = 0; c < kHeadDim / 32; ++c) {
+          uint32_t o[32];
+          ptx::tmem_ld32(tmem_o + c * 32, o);
+          ptx::tmem_wait_ld();
+          if (row_valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              const int col = c * 32 + i;
+              if (col < p.head_dim) {  // head_dim is a multiple of 8
+                uint4 w;
+                w.x = ptx::pack2<kBf16>(__uint_as_float(o[i + 0]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                w.y = ptx::pack2<kBf16>(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                w.z = ptx::pack2<kBf16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                w.w = ptx::pack2<kBf16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + col) = w;
+              }
+            }
+          }
+        }
+      }
+      if (row_valid) {
+        const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
+        const float lse = (l_run > 0.f) ? m_ref * p.lse_scale + __log2f(l_run) * kLn2 : -INFINITY;
+        const int64_t li = (p.cu_seqlens != nullptr)
+                               ? static_cast<int64_t>(it.h) * p.total + srow
+                               : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
+        p.lse[li] = lse;
+      }
+      ptx::tc_fence_before();
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == Cfg::kLoadWarp) ptx::tmem_dealloc(tmem, 512);
+}
+
+template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+int launch_fwd_instance(const FwdParams& p, int grid, cudaStream_t stream) {
+  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
+  auto kernel = fwd_kernel<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
+  static bool attr_set[16] = {false};
+  int dev = 0;
+  FDA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 16 && !attr_set[dev]) {
+    FDA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+  FDA_CUDA_TRY(cudaGetLastError());
+  return FDA_OK;
+}
+
+template <int kHeadDim, int kQTiles, int kStages>
+int dispatch_fwd(const FwdParams& p, int grid, bool bf16, bool softcap, cudaStream_t stream) {
+  if (bf16) {
+    return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, true, true>(p, grid, stream)
+                   : launch_fwd_instance<kHeadDim, kQTiles, kStages, true, false>(p, grid, stream);
+  }
+  return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, false, true>(p, grid, stream)
+                 : launch_fwd_instance<kHeadDim, kQTiles, kStages, false, false>(p, grid, stream);
+}
+
+}  // namespace
+
+int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
+  const FdaProblem& pr = a.p;
+  if (pr.dtype == FDA_E4M3) return FDA_ERR_UNSUPPORTED;
+  DeviceInfo info;
+  int rc = current_device_info(&info);
+  if (rc) return rc;
+  if (info.cc_major != 10) return FDA_ERR_ARCH;
+
+  const int d = pr.head_dim;
+  const int d_round = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
+  const int q_tiles = d_round <= 128 ? 2 : 1;
+  const bool varlen = pr.cu_seqlens != nullptr;
+  const int64_t rows = varlen ? pr.total : pr.seqlen;
+  const int tma_batch = varlen ? 1 : pr.batch;
+  const bool fp16 = pr.dtype == FDA_FP16;
+
+  FwdParams p;
+  memset(&p, 0, sizeof(p));
+  rc = encode_tile_map(&p.tm_q, a.q.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.q.row_stride,
+                       a.q.head_stride, a.q.batch_stride, 64, kBlockM);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_k, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
+                       a.k.head_stride, a.k.batch_stride, 64, kBlockN);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_v, a.v.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.v.row_stride,
+                       a.v.head_stride, a.v.batch_stride, 64, kBlockN);
+  if (rc) return rc;
+  p.out = a.out.ptr;
+  p.lse = a.lse;
+  p.o_batch_stride = varlen ? 0 : a.out.batch_stride;
+  p.o_row_stride = a.out.row_stride;
+  p.o_head_stride = a.out.head_stride;
+  p.cu_seqlens = pr.cu_seqlens;
+  p.batch = pr.batch;
+  p.seqlen = pr.seqlen;
+  p.total = pr.total;
+  p.heads = pr.heads;
+  p.heads_k = pr.heads_k;
+  p.head_dim = d;
+  p.block_size = pr.block_size;
+  const int max_n = pr.seqlen / 2;
+  p.items_per_half = ceil_div(max_n, q_tiles * kBlockM);
+  p.total_items = p.items_per_half * 2 * pr.heads * pr.batch;
+  const bool softcap = pr.softcap > 0.f;
+  if (softcap) {
+    p.scale_log2 = pr.softcap * kLog2e;
+    p.softcap_pre = pr.softmax_scale / pr.softcap;
+    p.lse_scale = pr.softcap;
+  } else {
+    p.scale_log2 = pr.softmax_scale * kLog2e;
+    p.softcap_pre = 0.f;
+    p.lse_scale = pr.softmax_scale;
+  }
+  if (p.total_items <= 0) return FDA_OK;
+  int grid = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
+  if (grid < 1) grid = 1;
+  if (grid > p.total_items) grid = p.total_items;
+  const bool bf16 = pr.dtype == FDA_BF16;
+  if (d_round == 64) return dispatch_fwd<64, 2, 6>(p, grid, bf16, softcap, stream);
+  if (d_round == 128) return dispatch_fwd<128, 2, 4>(p, grid, bf16, softcap, stream);
+  return dispatch_fwd<256, 1, 2>(p, grid, bf16, softcap, stream);
+}
+
+int read_status_fwd(int32_t* out4) {
+  int zero[4] = {0, 0, 0, 0};
+  FDA_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_fda_status, sizeof(int) * 4));
+  FDA_CUDA_TRY(cudaMemcpyToSymbol(g_fda_status, zero, sizeof(int) * 4));
+  return FDA_OK;
+}
+
+}  // namespace fda

@@ -1,0 +1,133 @@
+// Geometry of the block-diffusion mask: which key tiles a query tile visits, which query tiles a key tile
+// visits, and which of those need an element mask. Plain C++ (no CUDA types) so the same code runs in the
+// kernels and in host unit tests.
+//
+// A sample is [noisy half (n rows) | clean half (n rows)]; positions of a half are cut into blocks of `bs`
+// counted from the start of the half. half index: 0 = noisy, 1 = clean. Visibility (the reference states it
+// in csrc/fda/diffusion.h:6-19 and fast_diffusion_attention/reference.py:4-11):
+//   noisy i -> noisy j : same block           noisy i -> clean c : block(c) <  block(i)
+//   clean c -> clean c': block(c') <= block(c) clean -> noisy     : never
+// For a query the visible keys of one half are one interval, and so are the queries that see a key
+// (csrc/fda/diffusion.h:94-119 there gives the same intervals); both interval ends are non-decreasing in the
+// position, which is what the tile classification below relies on.
+#pragma once
+
+#if defined(__CUDACC__)
+#define FDA_HD __host__ __device__ __forceinline__
+#else
+#define FDA_HD inline
+#endif
+
+namespace fda {
+
+FDA_HD int imin(int a, int b) { return a < b ? a : b; }
+FDA_HD int imax(int a, int b) { return a > b ? a : b; }
+FDA_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Start / end (exclusive, clipped to n) of the block that holds position x of a half.
+FDA_HD int block_lo(int x, int bs) { return (x / bs) * bs; }
+FDA_HD int block_hi(int x, int bs, int n) { return imin((x / bs) * bs + bs, n); }
+
+// Keys of half kh visible from query position qi (< n) of half qh: [lo, hi). Empty for clean -> noisy.
+FDA_HD void key_interval(int qh, int kh, int qi, int n, int bs, int& lo, int& hi) {
+  const int b0 = block_lo(qi, bs);
+  const int b1 = imin(b0 + bs, n);
+  if (qh == 1) { lo = 0; hi = (kh == 1) ? b1 : 0; }
+  else if (kh == 1) { lo = 0; hi = b0; }
+  else { lo = b0; hi = b1; }
+}
+
+// Queries of half qh that see key position kj of half kh: [lo, hi). Empty if kj >= n or clean -> noisy.
+FDA_HD void query_interval(int qh, int kh, int kj, int n, int bs, int& lo, int& hi) {
+  if (kj >= n || (qh == 1 && kh == 0)) { lo = 0; hi = 0; return; }
+  const int b0 = block_lo(kj, bs);
+  if (kh == 1) { lo = (qh == 1) ? b0 : imin(b0 + bs, n); hi = n; }
+  else { lo = b0; hi = imin(b0 + bs, n); }
+}
+
+enum TileClass : int { kTileSkip = 0, kTileFull = 1, kTileMasked = 2 };
+
+// Classify the (query rows [qa, qb) of half qh) x (keys [k0, k0 + bn) of half kh) tile; qa < qb <= n.
+// Full: every query row sees every one of the bn keys (so all bn keys exist). Skip: nothing visible.
+// With need_full_rows (backward) a tile whose query rows stop short of `bm` rows is never "full", because
+// the padding rows must be masked out of the column sums.
+FDA_HD int classify_tile(int qh, int kh, int qa, int qb, int k0, int bn, int n, int bs,
+                         int bm = 0, bool need_full_rows = false) {
+  int lo_a, hi_a, lo_b, hi_b;
+  key_interval(qh, kh, qa, n, bs, lo_a, hi_a);
+  key_interval(qh, kh, qb - 1, n, bs, lo_b, hi_b);
+  const int k1 = k0 + bn;
+  // union over the rows is [lo_a, hi_b): the ends are non-decreasing in the row
+  if (k0 >= hi_b || k1 <= lo_a || hi_b <= lo_a) return kTileSkip;
+  // with several blocks inside the query tile a middle row may see keys the first and last do not, but a key
+  // tile between lo_a and hi_b always meets some row's interval, so "skip" above is exact for same-half
+  // noisy tiles too: consecutive blocks tile the key axis without gaps.
+  if (lo_b <= k0 && k1 <= hi_a && !(need_full_rows && (qb - qa) < bm)) return kTileFull;
+  return kTileMasked;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Forward-shaped enumeration (also used by the dQ kernel): key tiles visited by the query rows [qa, qb) of
+// half qh. Steps 0..n_clean-1 are clean key tiles 0.., the remaining n_noisy steps are noisy key tiles
+// noisy_lo.. (only for noisy queries). The reference enumerates the same set in csrc/fda/diffusion.h:134-183.
+// ---------------------------------------------------------------------------------------------------------
+struct KeyPlan {
+  int n_clean;
+  int noisy_lo;
+  int n_noisy;
+  FDA_HD int steps() const { return n_clean + n_noisy; }
+  FDA_HD void step(int s, int& kh, int& kt) const {
+    if (s < n_clean) { kh = 1; kt = s; } else { kh = 0; kt = noisy_lo + (s - n_clean); }
+  }
+};
+
+FDA_HD KeyPlan make_key_plan(int qh, int qa, int qb, int n, int bs, int bn) {
+  KeyPlan p;
+  const int last = qb - 1;
+  const int clean_hi = (qh == 1) ? block_hi(last, bs, n) : block_lo(last, bs);
+  p.n_clean = ceil_div(clean_hi, bn);
+  if (qh == 0) {
+    p.noisy_lo = block_lo(qa, bs) / bn;
+    p.n_noisy = ceil_div(block_hi(last, bs, n), bn) - p.noisy_lo;
+  } else {
+    p.noisy_lo = 0;
+    p.n_noisy = 0;
+  }
+  return p;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Backward (dK/dV-stationary) enumeration: query tiles of `bm` rows that see the keys [k0, k1) (k1 <= n) of
+// half kh. List 0 = query tiles of the same half, list 1 = noisy query tiles of later blocks (clean keys
+// only). The reference's equivalent is csrc/fda/diffusion.h:196-261.
+// ---------------------------------------------------------------------------------------------------------
+struct QueryPlan {
+  int same_lo, n_same;     // query tiles of half kh
+  int cross_lo, n_cross;   // noisy query tiles seeing clean keys
+  FDA_HD int steps() const { return n_same + n_cross; }
+  FDA_HD void step(int s, int kh, int& qh, int& qt) const {
+    if (s < n_same) { qh = kh; qt = same_lo + s; } else { qh = 0; qt = cross_lo + (s - n_same); }
+  }
+};
+
+FDA_HD QueryPlan make_query_plan(int kh, int k0, int k1, int n, int bs, int bm) {
+  QueryPlan p;
+  int lo, hi, lo2, hi2;
+  query_interval(kh, kh, k0, n, bs, lo, hi);
+  query_interval(kh, kh, k1 - 1, n, bs, lo2, hi2);
+  hi = imax(hi, hi2);
+  p.same_lo = lo / bm;
+  p.n_same = ceil_div(hi, bm) - p.same_lo;
+  p.cross_lo = 0;
+  p.n_cross = 0;
+  if (kh == 1) {
+    query_interval(0, 1, k0, n, bs, lo, hi);
+    if (lo < hi) {
+      p.cross_lo = lo / bm;
+      p.n_cross = ceil_div(hi, bm) - p.cross_lo;
+    }
+  }
+  return p;
+}
+
+}  // namespace fda

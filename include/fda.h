@@ -1,0 +1,138 @@
+/* C ABI of libfda_sm100: block-diffusion attention for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a host framework binds: plain pointers, sizes and element strides, no framework types.
+ * It stands where the reference project registers its torch operators `fda::fwd` and `fda::bwd`
+ * (csrc/fda/flash_api.cpp:645-682 there) and where its Python layer calls them
+ * (fast_diffusion_attention/interface.py:57 and :110).
+ *
+ * Conventions
+ *  - Every sample is [noisy half (n rows) | clean half (n rows)], 2n rows. Batched tensors are
+ *    (batch, 2n, heads, head_dim); packed ("varlen") tensors are (total, heads, head_dim) with
+ *    cu_seqlens (batch + 1 int32 on the device) and batch strides ignored.
+ *  - Strides are in ELEMENTS. The last dimension is contiguous. Row/head/batch strides of q, k, v (and of
+ *    dout in the backward) must be multiples of 16 bytes because the kernels fetch tiles with TMA.
+ *  - All pointers are device pointers on the current CUDA device. The library allocates nothing: outputs and
+ *    the workspace are the caller's. Work is enqueued on `stream` (a cudaStream_t); no host synchronisation.
+ *  - Return value 0 = success, otherwise an FdaStatus; fda_strerror() gives the message. Messages of argument
+ *    errors carry the same key words as the reference's checks (flash_api.cpp:96-137, :504-505).
+ */
+#ifndef FDA_H_
+#define FDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum FdaStatus {
+  FDA_OK = 0,
+  FDA_ERR_NULL = 1,            /* a required pointer is NULL */
+  FDA_ERR_DTYPE = 2,           /* unsupported dtype for this pass */
+  FDA_ERR_ODD_LENGTH = 3,      /* "The sequence length must be even" */
+  FDA_ERR_BLOCK_SIZE = 4,      /* "block_size must be a positive integer" */
+  FDA_ERR_HEAD_DIM = 5,        /* head_dim > 256 or not a multiple of 8 (16 for fp8) */
+  FDA_ERR_HEADS = 6,           /* heads % heads_k != 0 */
+  FDA_ERR_STRIDE = 7,          /* a stride is not a multiple of 16 bytes / last dim not contiguous */
+  FDA_ERR_DETERMINISTIC = 8,   /* kept for ABI stability: deterministic backward unsupported for this shape */
+  FDA_ERR_WORKSPACE = 9,       /* workspace missing or too small */
+  FDA_ERR_CUDA = 10,           /* a CUDA runtime / driver call failed; see fda_last_cuda_error() */
+  FDA_ERR_ARCH = 11,           /* the current device is not sm_100 */
+  FDA_ERR_UNSUPPORTED = 12,    /* feature combination not built */
+  FDA_ERR_SHAPE = 13,          /* inconsistent sizes */
+  FDA_ERR_DEVICE_WAIT = 14     /* a bounded device-side wait expired (reported by fda_device_status) */
+} FdaStatus;
+
+typedef enum FdaDtype { FDA_BF16 = 0, FDA_FP16 = 1, FDA_E4M3 = 2 } FdaDtype;
+
+/* One (rows, heads, head_dim) tensor view. */
+typedef struct FdaTensor {
+  void* ptr;
+  int64_t batch_stride; /* ignored when cu_seqlens != NULL */
+  int64_t row_stride;
+  int64_t head_stride;
+} FdaTensor;
+
+/* Problem description shared by forward and backward.
+ * Mirrors the fields of the reference's Qkv_params / Flash_fwd_params that are not sm90-specific
+ * (csrc/fda/flash.h:15-137). */
+typedef struct FdaProblem {
+  int32_t dtype;          /* FdaDtype of q, k, v */
+  int32_t batch;          /* number of samples */
+  int32_t seqlen;         /* 2n (batched) or the maximum sample length (varlen) */
+  int32_t total;          /* total rows: batch * seqlen (batched) or cu_seqlens[batch] (varlen) */
+  int32_t heads;          /* query heads */
+  int32_t heads_k;        /* key/value heads, divides heads */
+  int32_t head_dim;
+  int32_t block_size;     /* diffusion block size, >= 1 */
+  float softmax_scale;
+  float softcap;          /* 0 = off */
+  int32_t sm_margin;      /* SMs to leave free */
+  int32_t deterministic;  /* backward only: bitwise reproducible accumulation order */
+  const int32_t* cu_seqlens; /* device, batch + 1 entries, or NULL */
+} FdaProblem;
+
+/* Forward arguments; replaces mha_fwd (csrc/fda/flash_api.cpp:322-458).
+ * out: same dtype as q (bf16 for e4m3 inputs). lse: float32, (batch, heads, 2n) or (heads, total) for varlen,
+ * natural-log units. Descales: (batch, heads_k) float32 with the given strides, or NULL. */
+typedef struct FdaFwdArgs {
+  FdaProblem p;
+  FdaTensor q, k, v, out;
+  float* lse;
+  const float* q_descale; const float* k_descale; const float* v_descale;
+  int64_t descale_batch_stride[3];
+  int64_t descale_head_stride[3];
+  void* workspace;          /* fda_fwd_workspace_bytes() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+} FdaFwdArgs;
+
+/* Backward arguments; replaces mha_bwd (csrc/fda/flash_api.cpp:461-643).
+ * dq/dk/dv are written (not accumulated). lse is the forward's output. */
+typedef struct FdaBwdArgs {
+  FdaProblem p;
+  FdaTensor q, k, v, out, dout, dq, dk, dv;
+  const float* lse;
+  void* workspace;          /* fda_bwd_workspace_bytes() bytes, 256-byte aligned */
+  size_t workspace_bytes;
+} FdaBwdArgs;
+
+/* Workspace sizes (bytes) for a problem; never fails for valid sizes. Stand in for the allocations the
+ * reference makes inside mha_fwd / mha_bwd (flash_api.cpp:396-407, :565-572, :614-625). */
+size_t fda_fwd_workspace_bytes(const FdaProblem* p);
+size_t fda_bwd_workspace_bytes(const FdaProblem* p);
+
+/* Enqueue the forward / backward pass on `stream`. */
+int fda_fwd(const FdaFwdArgs* args, void* stream);
+int fda_bwd(const FdaBwdArgs* args, void* stream);
+
+/* Message for a status code. */
+const char* fda_strerror(int status);
+/* Last CUDA error string seen by this thread inside the library ("" if none). */
+const char* fda_last_cuda_error(void);
+
+/* Reads and clears the device status words (synchronises the device). out4 = {code, block, thread, detail};
+ * code 0 means no bounded wait has expired since the last call. Returns FDA_OK or FDA_ERR_DEVICE_WAIT. */
+int fda_device_status(int32_t* out4);
+
+/* Library version "major.minor.patch". */
+const char* fda_version(void);
+
+/* ---- host-only geometry probes (no GPU needed); used by the unit tests of the tile enumeration ---------- */
+/* Key tiles visited by query rows [qa, qb) of half qh: fills (key_half, key_tile) pairs, returns the count. */
+int fda_geom_key_plan(int qh, int qa, int qb, int n, int bs, int bn, int32_t* out_half, int32_t* out_tile, int cap);
+/* Query tiles visited by keys [k0, k1) of half kh. */
+int fda_geom_query_plan(int kh, int k0, int k1, int n, int bs, int bm, int32_t* out_half, int32_t* out_tile, int cap);
+/* 0 skip, 1 fully visible, 2 needs the element mask. */
+int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int bs, int bm, int need_full_rows);
+
+/* ---- tensor-core self test (GPU): C[128 x n] = A[128 x k] * B with the operand layouts the kernels use ---- */
+/* mode 0: A, B both K-major from shared memory; mode 1: A from tensor memory, B MN-major from shared memory;
+ * a, b, c are device pointers: a (128, k) bf16 row-major; b (n, k) bf16 row-major for mode 0, (k, n) row-major
+ * for mode 1; c (128, n) float32. k and n are multiples of 64, at most 128 (k) / 256 (n). */
+int fda_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDA_H_ */
