@@ -1,14 +1,899 @@
-// Backward pass (placeholder until the kernels land).
+// Backward pass of block-diffusion attention for sm_100a.
+//
+// The reference runs up to six launches (csrc/fda/flash_bwd_launch_template.h:26-284 there): a preprocess
+// (flash_bwd_preprocess_kernel.h:106-208), an optional noisy-diagonal kernel, the dK/dV-stationary main kernel
+// with an fp32 dQ accumulator reduced through global memory (mainloop_bwd_sm90_tma_gmma_ws.hpp:413-1014,
+// epilogue_bwd.hpp:25-441), and convert passes (flash_bwd_postprocess_kernel.h:160-264). On B200 the tensor
+// memory budget (512 columns) and the cost of a global fp32 reduction lead to a different split:
+//
+//   1. bwd_preprocess : delta = rowsum(dO * O) and LSE * log2(e), written to a padded per-(sample, head, half)
+//                       layout whose padding rows carry LSE2 = +inf (so padded query rows get P = 0).
+//   2. bwd_dkdv       : one CTA per (128-key tile, KV head, sample, half); K, V stay in shared memory, the
+//                       visible query tiles of every query head of the group stream through. S^T = K Q^T and
+//                       dP^T = V dO^T land in tensor memory (keys on lanes); P^T and dS^T go back to tensor
+//                       memory as 16-bit A operands of dV += P^T dO and dK += dS^T Q. GQA sums over the group
+//                       inside the CTA: no fp32 dK/dV accumulators in global memory.
+//   3. bwd_dq         : forward-shaped, one CTA per 128-row query tile: S = Q K^T, dP = dO V^T, dS to tensor
+//                       memory, dQ += dS K. No cross-CTA reduction at all, so dQ needs no atomics, no fp32
+//                       accumulator, no zero-fill and no convert pass.
+//
+// Seven GEMMs per tile pair instead of five, in exchange for zero global reductions; every gradient has a
+// fixed accumulation order, so the result is bitwise reproducible whether or not `deterministic` is set.
+// Numerics kept from the reference: P = exp2(S*c - LSE2) from the saved LSE, dS = P * (dP - delta)
+// [* (1 - tanh^2) with softcap, before masking], P and dS rounded to the input dtype before the second GEMMs,
+// dK and dQ scaled by softmax_scale once at the end (mainloop_bwd...hpp:836-893, :1009).
+#include "geometry.h"
 #include "host_util.h"
 #include "ptx.cuh"
 
 namespace fda {
-size_t bwd_workspace_bytes(const FdaProblem& p) { (void)p; return 256; }
-int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream) { (void)a; (void)stream; return FDA_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int kTile = 128;  // rows of every query / key tile
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  CUtensorMap tm_q, tm_k, tm_v, tm_do;
+  const void* out;
+  const void* dout;
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t o_bs, o_rs, o_hs;
+  int64_t do_bs, do_rs, do_hs;
+  int64_t dq_bs, dq_rs, dq_hs;
+  int64_t dk_bs, dk_rs, dk_hs;
+  int64_t dv_bs, dv_rs, dv_hs;
+  const float* lse;
+  float* delta_pad;  // (batch, heads, 2, n_pad)
+  float* lse2_pad;   // (batch, heads, 2, n_pad)
+  const int32_t* cu_seqlens;
+  int batch, seqlen, total, heads, heads_k, head_dim, block_size;
+  int n_pad;           // round_up(max n, 128)
+  int tiles_per_half;  // n_pad / 128
+  float scale_log2, softcap_pre, softmax_scale;
+};
+
+struct Sample {
+  int n, row0, bcoord;
+};
+
+__device__ __forceinline__ Sample sample_of(const BwdParams& p, int b) {
+  Sample s;
+  if (p.cu_seqlens != nullptr) {
+    const int lo = p.cu_seqlens[b];
+    s.n = (p.cu_seqlens[b + 1] - lo) / 2;
+    s.row0 = lo;
+    s.bcoord = 0;
+  } else {
+    s.n = p.seqlen / 2;
+    s.row0 = 0;
+    s.bcoord = b;
+  }
+  return s;
+}
+
+__device__ __forceinline__ int64_t stat_segment(const BwdParams& p, int b, int h, int half) {
+  return ((static_cast<int64_t>(b) * p.heads + h) * 2 + half) * p.n_pad;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 1. preprocess
+// ------------------------------------------------------------------------------------------------------------
+template <bool kBf16, int kLanes>
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(const __grid_constant__ BwdParams p) {
+  constexpr int kRowsPerWarp = 32 / kLanes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / kLanes, l = lane % kLanes;
+  const int r = (blockIdx.x * 8 + warp) * kRowsPerWarp + sub;  // position in the half, < n_pad
+  const int hh = blockIdx.y;
+  const int h = hh >> 1, half = hh & 1;
+  const int b = blockIdx.z;
+  if (r >= p.n_pad) return;
+  const Sample sm = sample_of(p, b);
+  const int64_t seg = stat_segment(p, b, h, half);
+  float acc = 0.f;
+  const bool valid = r < sm.n;
+  int64_t srow = 0;
+  if (valid) {
+    srow = static_cast<int64_t>(sm.row0) + half * sm.n + r;
+    const uint16_t* o = static_cast<const uint16_t*>(p.out) + sm.bcoord * p.o_bs + srow * p.o_rs + h * p.o_hs;
+    const uint16_t* g = static_cast<const uint16_t*>(p.dout) + sm.bcoord * p.do_bs + srow * p.do_rs + h * p.do_hs;
+    for (int c = l * 8; c < p.head_dim; c += kLanes * 8) {
+      const uint4 a = *reinterpret_cast<const uint4*>(o + c);
+      const uint4 d = *reinterpret_cast<const uint4*>(g + c);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 fa, fd;
+        if (kBf16) {
+          fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+          fd = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[i]));
+        } else {
+          fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+          fd = __half22float2(*reinterpret_cast<const __half2*>(&dw[i]));
+        }
+        acc = fmaf(fa.x, fd.x, acc);
+        acc = fmaf(fa.y, fd.y, acc);
+      }
+    }
+  }
+#pragma unroll
+  for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (l == 0) {
+    float lse2 = INFINITY;
+    if (valid) {
+      const int64_t li = (p.cu_seqlens != nullptr)
+                             ? static_cast<int64_t>(h) * p.total + srow
+                             : (static_cast<int64_t>(b) * p.heads + h) * p.seqlen + (half * sm.n + r);
+      const float lse = p.lse[li];
+      lse2 = (lse == -INFINITY) ? 0.f : lse * kLog2e;
+    }
+    p.delta_pad[seg + r] = valid ? acc : 0.f;
+    p.lse2_pad[seg + r] = lse2;
+  }
+}
+
+// Shared-memory layout helpers ------------------------------------------------------------------------------------
+template <int kHeadDim>
+struct TileCfg {
+  static constexpr int kTileBytes = kTile * kHeadDim * 2;
+  static constexpr int kPanels = kHeadDim / 64;
+  static constexpr int kPanelBytes = 128 * 128;
+};
+
+template <int kHeadDim>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row, int head,
+                                          int bcoord) {
+#pragma unroll
+  for (int c = 0; c < TileCfg<kHeadDim>::kPanels; ++c) {
+    ptx::tma_load_4d(dst + c * TileCfg<kHeadDim>::kPanelBytes, tm, bar, c * 64, row, head, bcoord);
+  }
+}
+
+// D[tmem, 128 x 128] = A[smem tile, rows x d] * B[smem tile, rows x d]^T, both K-major along d.
+template <int kHeadDim>
+__device__ __forceinline__ void mma_rows_x_rows(uint32_t d_tmem, const uint8_t* a_tile, const uint8_t* b_tile,
+                                                uint32_t idesc) {
+  const uint32_t a0 = ptx::smem_u32(a_tile), b0 = ptx::smem_u32(b_tile);
+#pragma unroll
+  for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+    const uint32_t off = (kk / 4) * TileCfg<kHeadDim>::kPanelBytes + (kk % 4) * 32;
+    ptx::umma_ss_f16(d_tmem, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc,
+                     kk > 0);
+  }
+}
+
+// D[tmem, 128 x d] (+)= A[tmem, 128 x 128 as 16-bit] * B[smem tile, 128 rows x d] (B MN-major: rows are the
+// reduction dimension). The A operand sits in two 32-column pieces: reduction rows 0-63 at a_tmem, 64-127 at
+// a_tmem + a_second_half.
+template <int kHeadDim>
+__device__ __forceinline__ void mma_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t a_second_half,
+                                                const uint8_t* b_tile, uint32_t idesc, bool accumulate) {
+  const uint32_t b0 = ptx::smem_u32(b_tile);
+#pragma unroll
+  for (int kk = 0; kk < kTile / 16; ++kk) {
+    const uint32_t a = a_tmem + (kk < 4 ? kk * 8 : a_second_half + (kk - 4) * 8);
+    ptx::umma_ts_f16(d_tmem, a, ptx::make_smem_desc(b0 + kk * 2048, TileCfg<kHeadDim>::kPanelBytes, 1024), idesc,
+                     (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+// Store 32 fp32 accumulator columns of one row, scaled, as 16-bit, honouring head_dim.
+template <bool kBf16>
+__device__ __forceinline__ void store_row_chunk(uint16_t* row_ptr, int col0, const uint32_t* acc, float scale,
+                                                int head_dim) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    const int col = col0 + i;
+    if (col < head_dim) {
+      uint4 w;
+      w.x = ptx::pack2<kBf16>(__uint_as_float(acc[i + 0]) * scale, __uint_as_float(acc[i + 1]) * scale);
+      w.y = ptx::pack2<kBf16>(__uint_as_float(acc[i + 2]) * scale, __uint_as_float(acc[i + 3]) * scale);
+      w.z = ptx::pack2<kBf16>(__uint_as_float(acc[i + 4]) * scale, __uint_as_float(acc[i + 5]) * scale);
+      w.w = ptx::pack2<kBf16>(__uint_as_float(acc[i + 6]) * scale, __uint_as_float(acc[i + 7]) * scale);
+      *reinterpret_cast<uint4*>(row_ptr + col) = w;
+    }
+  }
+}
+
+// P and dS of 64 columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
+// lse2 / delta are per column (kPerColumn, read from shared memory) or per thread.
+template <bool kBf16, bool kSoftcap, bool kPerColumn>
+__device__ __forceinline__ void softmax_backward_64(const uint32_t* s, const uint32_t* dp, const float* lse2_col,
+                                                    const float* delta_col, float lse2_row, float delta_row,
+                                                    float scale_log2, float softcap_pre, bool masked, int lo,
+                                                    int hi, uint32_t* pk_p, uint32_t* pk_ds) {
+#pragma unroll
+  for (int c = 0; c < 64; c += 2) {
+    float pv[2], dsv[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = c + e;
+      float x = __uint_as_float(s[col]);
+      float dt = 1.f;
+      if (kSoftcap) {
+        x = ptx::tanh_fast(x * softcap_pre);
+        dt = 1.f - x * x;
+      }
+      const float l2 = kPerColumn ? lse2_col[col] : lse2_row;
+      const float dl = kPerColumn ? delta_col[col] : delta_row;
+      float pr = ptx::ex2(fmaf(x, scale_log2, -l2));
+      float d = pr * (__uint_as_float(dp[col]) - dl);
+      if (kSoftcap) d *= dt;
+      if (masked && (col < lo || col >= hi)) {
+        pr = 0.f;
+        d = 0.f;
+      }
+      pv[e] = pr;
+      dsv[e] = d;
+    }
+    pk_p[c / 2] = ptx::pack2<kBf16>(pv[0], pv[1]);
+    pk_ds[c / 2] = ptx::pack2<kBf16>(dsv[0], dsv[1]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 2. dK / dV
+// ------------------------------------------------------------------------------------------------------------
+struct KvItem {
+  int b, hk, kh, k0, k1, n, row0, bcoord;
+  bool valid;
+};
+
+__device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
+  KvItem it;
+  const int per_tile = 2 * p.heads_k * p.batch;
+  const int kt = idx / per_tile;  // ascending: early clean key tiles are seen by the most queries
+  const int rem = idx - kt * per_tile;
+  it.kh = 1 - (rem & 1);          // clean first
+  const int bh = rem >> 1;
+  it.b = bh / p.heads_k;
+  it.hk = bh - it.b * p.heads_k;
+  const Sample sm = sample_of(p, it.b);
+  it.n = sm.n;
+  it.row0 = sm.row0;
+  it.bcoord = sm.bcoord;
+  it.k0 = kt * kTile;
+  it.valid = it.k0 < it.n;
+  it.k1 = imin(it.k0 + kTile, it.n);
+  return it;
+}
+
+template <int kHeadDim, int kStages>
+struct DkdvCfg {
+  using T = TileCfg<kHeadDim>;
+  static constexpr int kStageBytes = 2 * T::kTileBytes + 1024;  // Q tile, dO tile, lse2[128], delta[128]
+  static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 256;
+  static constexpr int kThreads = 320;
+  static constexpr int kTmemST = 0, kTmemDPT = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
+  static_assert(256 + 2 * kHeadDim <= 512, "tensor memory budget");
+};
+
+template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
+__global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
+  using Cfg = DkdvCfg<kHeadDim, kStages>;
+  using T = TileCfg<kHeadDim>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + T::kTileBytes;
+  uint8_t* sStage = smem + 2 * T::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStage + kStages * Cfg::kStageBytes);
+  uint64_t* kv_full = bars;
+  uint64_t* kv_empty = bars + 1;
+  uint64_t* st_full = bars + 2;
+  uint64_t* st_empty = st_full + kStages;
+  uint64_t* sdp_full = st_empty + kStages;
+  uint64_t* pds_full = sdp_full + 1;
+  uint64_t* acc_full = pds_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(kv_full, 1);
+    ptx::mbar_init(kv_empty, 1);
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&st_full[i], 1);
+      ptx::mbar_init(&st_empty[i], 1);
+    }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(pds_full, 256);
+    ptx::mbar_init(acc_full, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int bs = p.block_size;
+  const int group = p.heads / p.heads_k;
+  const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t n_item = 0, slot = 0;
+      bool alive = true;
+      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+        const KvItem it = decode_kv_item(p, idx);
+        if (!it.valid) continue;
+        const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+        if (!ptx::mbar_wait(kv_empty, (n_item & 1) ^ 1, abort_flag, 41)) break;
+        ptx::mbar_expect_tx(kv_full, 2 * T::kTileBytes);
+        const int k_row = it.row0 + it.kh * it.n + it.k0;
+        load_tile<kHeadDim>(sK, &p.tm_k, kv_full, k_row, it.hk, it.bcoord);
+        load_tile<kHeadDim>(sV, &p.tm_v, kv_full, k_row, it.hk, it.bcoord);
+        for (int g = 0; g < group && alive; ++g) {
+          const int h = it.hk * group + g;
+          for (int s = 0; s < plan.steps(); ++s) {
+            int qh, qt;
+            plan.step(s, it.kh, qh, qt);
+            const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
+            if (classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs) == kTileSkip) continue;
+            const uint32_t stage = slot % kStages;
+            if (!ptx::mbar_wait(&st_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 42)) { alive = false; break; }
+            uint8_t* base = sStage + stage * Cfg::kStageBytes;
+            ptx::mbar_expect_tx(&st_full[stage], 2 * T::kTileBytes + 1024);
+            const int q_row = it.row0 + qh * it.n + qa;
+            load_tile<kHeadDim>(base, &p.tm_q, &st_full[stage], q_row, h, it.bcoord);
+            load_tile<kHeadDim>(base + T::kTileBytes, &p.tm_do, &st_full[stage], q_row, h, it.bcoord);
+            const int64_t seg = stat_segment(p, it.b, h, qh) + qa;
+            ptx::bulk_load_1d(base + 2 * T::kTileBytes, p.lse2_pad + seg, 512, &st_full[stage]);
+            ptx::bulk_load_1d(base + 2 * T::kTileBytes + 512, p.delta_pad + seg, 512, &st_full[stage]);
+            ++slot;
+          }
+        }
+        ++n_item;
+      }
+      if (*abort_flag) __nanosleep(100000);
+    }
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr int kFmt = kBf16 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
+      const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      uint32_t n_item = 0, slot = 0, cnt = 0;
+      bool alive = true;
+      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+        const KvItem it = decode_kv_item(p, idx);
+        if (!it.valid) continue;
+        const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+        if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
+        bool acc = false;
+        for (int g = 0; g < group && alive; ++g) {
+          for (int s = 0; s < plan.steps(); ++s) {
+            int qh, qt;
+            plan.step(s, it.kh, qh, qt);
+            const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
+            if (classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs) == kTileSkip) continue;
+            const uint32_t stage = slot % kStages;
+            if (!ptx::mbar_wait(&st_full[stage], (slot / kStages) & 1, abort_flag, 52)) { alive = false; break; }
+            ptx::tc_fence_after();
+            const uint8_t* sQ = sStage + stage * Cfg::kStageBytes;
+            const uint8_t* sdO = sQ + T::kTileBytes;
+            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemST, sK, sQ, idesc_s);
+            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDPT, sV, sdO, idesc_s);
+            ptx::umma_commit(sdp_full);
+            if (!ptx::mbar_wait(pds_full, cnt & 1, abort_flag, 53)) { alive = false; break; }
+            ++cnt;
+            ptx::tc_fence_after();
+            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDV, tmem + Cfg::kTmemST, 64, sdO, idesc_g, acc);
+            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDK, tmem + Cfg::kTmemDPT, 64, sQ, idesc_g, acc);
+            acc = true;
+            ptx::umma_commit(&st_empty[stage]);
+            ++slot;
+          }
+        }
+        if (!alive) break;
+        ptx::umma_commit(kv_empty);
+        ptx::umma_commit(acc_full);
+        ++n_item;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------- softmax backward + epilogue
+    const int wg = warp >> 2;                  // which 64 query columns
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;          // key row inside the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint32_t n_item = 0, slot = 0, cnt = 0;
+    bool alive = true;
+    for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      const KvItem it = decode_kv_item(p, idx);
+      if (!it.valid) continue;
+      const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+      const int kj = it.k0 + row;
+      for (int g = 0; g < group && alive; ++g) {
+        for (int s = 0; s < plan.steps(); ++s) {
+          int qh, qt;
+          plan.step(s, it.kh, qh, qt);
+          const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
+          const int cls = classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs);
+          if (cls == kTileSkip) continue;
+          const uint32_t stage = slot % kStages;
+          ++slot;
+          int lo = 0, hi = 0;
+          if (cls == kTileMasked) {
+            query_interval(qh, it.kh, kj, it.n, bs, lo, hi);
+            lo -= qa + wg * 64;
+            hi -= qa + wg * 64;
+          }
+          const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * T::kTileBytes);
+          // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
+          if (!ptx::mbar_wait(&st_full[stage], ((slot - 1) / kStages) & 1, abort_flag, 60)) { alive = false; break; }
+          if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 61)) { alive = false; break; }
+          ++cnt;
+          ptx::tc_fence_after();
+          uint32_t sv[64], dpv[64];
+          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * 64, sv);
+          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * 64 + 32, sv + 32);
+          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64, dpv);
+          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64 + 32, dpv + 32);
+          ptx::tmem_wait_ld();
+          uint32_t pk_p[32], pk_ds[32];
+          softmax_backward_64<kBf16, kSoftcap, true>(sv, dpv, stats + wg * 64, stats + 128 + wg * 64, 0.f, 0.f,
+                                                     p.scale_log2, p.softcap_pre, cls == kTileMasked, lo, hi, pk_p,
+                                                     pk_ds);
+          // every warp of this warpgroup has its S^T / dP^T in registers only after its own loads; the two
+          // warpgroups write disjoint 32-column pieces inside their own 64 columns
+          ptx::tmem_st32(tmem + Cfg::kTmemST + lane_addr + wg * 64, pk_p);
+          ptx::tmem_st32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64, pk_ds);
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(pds_full);
+        }
+      }
+      if (!alive) break;
+      if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
+      ++n_item;
+      ptx::tc_fence_after();
+      {
+        const bool key_valid = kj < it.n;
+        const int64_t srow = static_cast<int64_t>(it.row0) + it.kh * it.n + kj;
+        uint16_t* dst;
+        uint32_t src;
+        float scale;
+        if (wg == 0) {
+          dst = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
+          src = tmem + Cfg::kTmemDK + lane_addr;
+          scale = p.softmax_scale;
+        } else {
+          dst = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
+          src = tmem + Cfg::kTmemDV + lane_addr;
+          scale = 1.f;
+        }
+#pragma unroll
+        for (int c = 0; c < kHeadDim / 32; ++c) {
+          uint32_t acc[32];
+          ptx::tmem_ld32(src + c * 32, acc);
+          ptx::tmem_wait_ld();
+          if (key_valid) store_row_chunk<kBf16>(dst, c * 32, acc, scale, p.head_dim);
+        }
+      }
+      ptx::tc_fence_before();
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// 3. dQ
+// ------------------------------------------------------------------------------------------------------------
+struct QItem {
+  int b, h, hk, qh, qa, qb, n, row0, bcoord;
+  bool valid;
+};
+
+__device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
+  QItem it;
+  const int per_tile = 2 * p.heads * p.batch;
+  const int t_rev = idx / per_tile;
+  const int rem = idx - t_rev * per_tile;
+  it.qh = rem & 1;
+  const int bh = rem >> 1;
+  it.b = bh / p.heads;
+  it.h = bh - it.b * p.heads;
+  it.hk = it.h / (p.heads / p.heads_k);
+  const Sample sm = sample_of(p, it.b);
+  it.n = sm.n;
+  it.row0 = sm.row0;
+  it.bcoord = sm.bcoord;
+  it.qa = (p.tiles_per_half - 1 - t_rev) * kTile;  // late query tiles see the most keys: longest first
+  it.valid = it.qa < it.n;
+  it.qb = imin(it.qa + kTile, it.n);
+  return it;
+}
+
+template <int kHeadDim, int kStages>
+struct DqCfg {
+  using T = TileCfg<kHeadDim>;
+  static constexpr int kSmemBytes = (2 + kStages) * T::kTileBytes + 1024 + 256;
+  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDS = 256, kTmemDQ = 384;
+  static_assert(384 + kHeadDim <= 512, "tensor memory budget");
+};
+
+template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
+__global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
+  using Cfg = DqCfg<kHeadDim, kStages>;
+  using T = TileCfg<kHeadDim>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + T::kTileBytes;
+  uint8_t* sKV = smem + 2 * T::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * T::kTileBytes);
+  uint64_t* q_full = bars;
+  uint64_t* q_empty = bars + 1;
+  uint64_t* kv_full = bars + 2;
+  uint64_t* kv_empty = kv_full + kStages;
+  uint64_t* sdp_full = kv_empty + kStages;
+  uint64_t* sdp_free = sdp_full + 1;
+  uint64_t* ds_full = sdp_free + 1;
+  uint64_t* ds_free = ds_full + 1;
+  uint64_t* dq_full = ds_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    ptx::mbar_init(q_full, 1);
+    ptx::mbar_init(q_empty, 1);
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&kv_full[i], 1);
+      ptx::mbar_init(&kv_empty[i], 1);
+    }
+    ptx::mbar_init(sdp_full, 1);
+    ptx::mbar_init(sdp_free, 256);
+    ptx::mbar_init(ds_full, 256);
+    ptx::mbar_init(ds_free, 1);
+    ptx::mbar_init(dq_full, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int bs = p.block_size;
+  const int total_items = p.tiles_per_half * 2 * p.heads * p.batch;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      uint32_t n_item = 0, slot = 0;
+      bool alive = true;
+      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+        const QItem it = decode_q_item(p, idx);
+        if (!it.valid) continue;
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 71)) break;
+        ptx::mbar_expect_tx(q_full, 2 * T::kTileBytes);
+        const int q_row = it.row0 + it.qh * it.n + it.qa;
+        load_tile<kHeadDim>(sQ, &p.tm_q, q_full, q_row, it.h, it.bcoord);
+        load_tile<kHeadDim>(sdO, &p.tm_do, q_full, q_row, it.h, it.bcoord);
+        for (int s = 0; s < plan.steps() && alive; ++s) {
+          int kh, kt;
+          plan.step(s, kh, kt);
+          if (classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs) == kTileSkip) continue;
+          const int k_row = it.row0 + kh * it.n + kt * kTile;
+          for (int which = 0; which < 2; ++which) {
+            const uint32_t stage = slot % kStages;
+            if (!ptx::mbar_wait(&kv_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 72)) { alive = false; break; }
+            ptx::mbar_expect_tx(&kv_full[stage], T::kTileBytes);
+            load_tile<kHeadDim>(sKV + stage * T::kTileBytes, which == 0 ? &p.tm_k : &p.tm_v, &kv_full[stage], k_row,
+                                it.hk, it.bcoord);
+            ++slot;
+          }
+        }
+        ++n_item;
+      }
+      if (*abort_flag) __nanosleep(100000);
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr int kFmt = kBf16 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
+      const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      uint32_t n_item = 0, slot = 0, cnt_sdp = 0, cnt_ds = 0;
+      bool alive = true;
+      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+        const QItem it = decode_q_item(p, idx);
+        if (!it.valid) continue;
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        int active = 0;
+        for (int s = 0; s < plan.steps(); ++s) {
+          int kh, kt;
+          plan.step(s, kh, kt);
+          active += classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs) != kTileSkip;
+        }
+        if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
+        // S/dP of step j+1 are issued before dQ of step j so the tensor pipe has work during the softmax math
+        auto issue_sdp = [&](uint32_t slot_k) -> bool {
+          if (!ptx::mbar_wait(sdp_free, (cnt_sdp & 1) ^ 1, abort_flag, 82)) return false;
+          ++cnt_sdp;
+          if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 83)) return false;
+          if (!ptx::mbar_wait(&kv_full[(slot_k + 1) % kStages], ((slot_k + 1) / kStages) & 1, abort_flag, 84)) return false;
+          ptx::tc_fence_after();
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, sQ, sKV + (slot_k % kStages) * T::kTileBytes, idesc_s);
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, sdO, sKV + ((slot_k + 1) % kStages) * T::kTileBytes, idesc_s);
+          ptx::umma_commit(sdp_full);
+          ptx::umma_commit(&kv_empty[(slot_k + 1) % kStages]);  // V tile no longer needed
+          return true;
+        };
+        if (!issue_sdp(slot)) break;
+        for (int j = 0; j < active && alive; ++j) {
+          const uint32_t slot_k = slot + 2 * j;
+          if (j + 1 < active) {
+            if (!issue_sdp(slot_k + 2)) { alive = false; break; }
+          }
+          if (!ptx::mbar_wait(ds_full, cnt_ds & 1, abort_flag, 85)) { alive = false; break; }
+          ++cnt_ds;
+          ptx::tc_fence_after();
+          mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS, 32, sKV + (slot_k % kStages) * T::kTileBytes,
+                                    idesc_g, j > 0);
+          ptx::umma_commit(&kv_empty[slot_k % kStages]);
+          ptx::umma_commit(ds_free);
+        }
+        if (!alive) break;
+        ptx::umma_commit(q_empty);
+        ptx::umma_commit(dq_full);
+        slot += 2 * active;
+        ++n_item;
+      }
+    }
+  } else {
+    const int wg = warp >> 2;                  // which 64 key columns
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;          // query row inside the tile
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint32_t n_item = 0, cnt = 0;
+    bool alive = true;
+    for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      const QItem it = decode_q_item(p, idx);
+      if (!it.valid) continue;
+      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+      const int r = it.qa + row;
+      const bool row_valid = r < it.n;
+      const int r_eff = row_valid ? r : it.n - 1;
+      const int blk0 = block_lo(r_eff, bs);
+      const int blk1 = imin(blk0 + bs, it.n);
+      const int64_t seg = stat_segment(p, it.b, it.h, it.qh);
+      const float lse2 = p.lse2_pad[seg + r];
+      const float delta = p.delta_pad[seg + r];
+      for (int s = 0; s < plan.steps() && alive; ++s) {
+        int kh, kt;
+        plan.step(s, kh, kt);
+        const int cls = classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs);
+        if (cls == kTileSkip) continue;
+        int lo = 0, hi = 0;
+        if (cls == kTileMasked) {
+          if (it.qh == 1) { lo = 0; hi = blk1; }
+          else if (kh == 1) { lo = 0; hi = blk0; }
+          else { lo = blk0; hi = blk1; }
+          lo -= kt * kTile + wg * 64;
+          hi -= kt * kTile + wg * 64;
+        }
+        if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 91)) { alive = false; break; }
+        ptx::tc_fence_after();
+        uint32_t sv[64], dpv[64];
+        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * 64, sv);
+        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * 64 + 32, sv + 32);
+        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * 64, dpv);
+        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * 64 + 32, dpv + 32);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(sdp_free);
+        uint32_t pk_p[32], pk_ds[32];
+        softmax_backward_64<kBf16, kSoftcap, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
+                                                    p.softcap_pre, cls == kTileMasked, lo, hi, pk_p, pk_ds);
+        if (!ptx::mbar_wait(ds_free, (cnt & 1) ^ 1, abort_flag, 92)) { alive = false; break; }
+        ++cnt;
+        ptx::tc_fence_after();
+        ptx::tmem_st32(tmem + Cfg::kTmemDS + lane_addr + wg * 32, pk_ds);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(ds_full);
+      }
+      if (!alive) break;
+      if (!ptx::mbar_wait(dq_full, n_item & 1, abort_flag, 93)) break;
+      ++n_item;
+      ptx::tc_fence_after();
+      {
+        const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
+        uint16_t* dst = static_cast<uint16_t*>(p.dq) + it.bcoord * p.dq_bs + srow * p.dq_rs + it.h * p.dq_hs;
+        constexpr int kChunks = kHeadDim / 64;  // 32-column chunks per warpgroup
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          const int col0 = (wg * kChunks + c) * 32;
+          uint32_t acc[32];
+          ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + col0, acc);
+          ptx::tmem_wait_ld();
+          if (row_valid) store_row_chunk<kBf16>(dst, col0, acc, p.softmax_scale, p.head_dim);
+        }
+      }
+      ptx::tc_fence_before();
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+}
+
+template <typename Kernel>
+int set_smem(Kernel kernel, int bytes, bool* done) {
+  int dev = 0;
+  FDA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 16 && !done[dev]) {
+    FDA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[dev] = true;
+  }
+  return FDA_OK;
+}
+
+template <int kHeadDim, int kStagesKv, int kStagesQ, bool kBf16, bool kSoftcap>
+int launch_bwd_instance(const BwdParams& p, int sm_count, cudaStream_t stream) {
+  {
+    using Cfg = DkdvCfg<kHeadDim, kStagesKv>;
+    auto kernel = bwd_dkdv_kernel<kHeadDim, kStagesKv, kBf16, kSoftcap>;
+    static bool done[16] = {false};
+    int rc = set_smem(kernel, Cfg::kSmemBytes, done);
+    if (rc) return rc;
+    const int items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+    const int grid = items < sm_count ? items : sm_count;
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+    FDA_CUDA_TRY(cudaGetLastError());
+  }
+  {
+    using Cfg = DqCfg<kHeadDim, kStagesQ>;
+    auto kernel = bwd_dq_kernel<kHeadDim, kStagesQ, kBf16, kSoftcap>;
+    static bool done[16] = {false};
+    int rc = set_smem(kernel, Cfg::kSmemBytes, done);
+    if (rc) return rc;
+    const int items = p.tiles_per_half * 2 * p.heads * p.batch;
+    const int grid = items < sm_count ? items : sm_count;
+    kernel<<<grid, 320, Cfg::kSmemBytes, stream>>>(p);
+    FDA_CUDA_TRY(cudaGetLastError());
+  }
+  return FDA_OK;
+}
+
+template <int kHeadDim, int kStagesKv, int kStagesQ>
+int dispatch_bwd(const BwdParams& p, int sm_count, bool bf16, bool softcap, cudaStream_t stream) {
+  if (bf16) {
+    return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, true>(p, sm_count, stream)
+                   : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, false>(p, sm_count, stream);
+  }
+  return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, true>(p, sm_count, stream)
+                 : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, false>(p, sm_count, stream);
+}
+
+inline int64_t round_up64(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+}  // namespace
+
+// Workspace: delta_pad then lse2_pad, each batch * heads * 2 * n_pad floats (256-byte aligned pieces).
+size_t bwd_workspace_bytes(const FdaProblem& pr) {
+  const int64_t n_pad = round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile);
+  const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * n_pad * 4, 256);
+  return static_cast<size_t>(2 * one + 256);
+}
+
+int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream) {
+  const FdaProblem& pr = a.p;
+  DeviceInfo info;
+  int rc = current_device_info(&info);
+  if (rc) return rc;
+  if (info.cc_major != 10) return FDA_ERR_ARCH;
+  const int d = pr.head_dim;
+  if (d > 128) return FDA_ERR_UNSUPPORTED;
+  const int d_round = d <= 64 ? 64 : 128;
+  const bool varlen = pr.cu_seqlens != nullptr;
+  const int64_t rows = varlen ? pr.total : pr.seqlen;
+  const int tma_batch = varlen ? 1 : pr.batch;
+  const bool fp16 = pr.dtype == FDA_FP16;
+
+  BwdParams p;
+  memset(&p, 0, sizeof(p));
+  rc = encode_tile_map(&p.tm_q, a.q.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.q.row_stride,
+                       a.q.head_stride, a.q.batch_stride, 64, kTile);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_do, a.dout.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.dout.row_stride,
+                       a.dout.head_stride, a.dout.batch_stride, 64, kTile);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_k, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
+                       a.k.head_stride, a.k.batch_stride, 64, kTile);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_v, a.v.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.v.row_stride,
+                       a.v.head_stride, a.v.batch_stride, 64, kTile);
+  if (rc) return rc;
+  // the preprocess and the epilogues use 16-byte vector accesses on rows of out / dout / dq / dk / dv
+  const FdaTensor* vec[] = {&a.out, &a.dout, &a.dq, &a.dk, &a.dv};
+  for (const FdaTensor* t : vec) {
+    if ((reinterpret_cast<uintptr_t>(t->ptr) & 15) || (t->row_stride % 8) || (t->head_stride % 8) ||
+        (!varlen && (t->batch_stride % 8))) {
+      return FDA_ERR_STRIDE;
+    }
+  }
+  p.out = a.out.ptr;
+  p.dout = a.dout.ptr;
+  p.dq = a.dq.ptr;
+  p.dk = a.dk.ptr;
+  p.dv = a.dv.ptr;
+  auto set3 = [&](const FdaTensor& t, int64_t& bs_, int64_t& rs_, int64_t& hs_) {
+    bs_ = varlen ? 0 : t.batch_stride;
+    rs_ = t.row_stride;
+    hs_ = t.head_stride;
+  };
+  set3(a.out, p.o_bs, p.o_rs, p.o_hs);
+  set3(a.dout, p.do_bs, p.do_rs, p.do_hs);
+  set3(a.dq, p.dq_bs, p.dq_rs, p.dq_hs);
+  set3(a.dk, p.dk_bs, p.dk_rs, p.dk_hs);
+  set3(a.dv, p.dv_bs, p.dv_rs, p.dv_hs);
+  p.lse = a.lse;
+  p.cu_seqlens = pr.cu_seqlens;
+  p.batch = pr.batch;
+  p.seqlen = pr.seqlen;
+  p.total = pr.total;
+  p.heads = pr.heads;
+  p.heads_k = pr.heads_k;
+  p.head_dim = d;
+  p.block_size = pr.block_size;
+  p.n_pad = static_cast<int>(round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile));
+  p.tiles_per_half = p.n_pad / kTile;
+  const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * p.n_pad * 4, 256);
+  p.delta_pad = static_cast<float*>(a.workspace);
+  p.lse2_pad = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + one);
+  const bool softcap = pr.softcap > 0.f;
+  p.softmax_scale = pr.softmax_scale;
+  if (softcap) {
+    p.scale_log2 = pr.softcap * kLog2e;
+    p.softcap_pre = pr.softmax_scale / pr.softcap;
+  } else {
+    p.scale_log2 = pr.softmax_scale * kLog2e;
+    p.softcap_pre = 0.f;
+  }
+  int sm_count = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
+  if (sm_count < 1) sm_count = 1;
+  const bool bf16 = pr.dtype == FDA_BF16;
+
+  {
+    const int lanes = d <= 64 ? 8 : (d <= 128 ? 16 : 32);
+    const int rows_per_block = 8 * (32 / lanes);
+    dim3 grid((p.n_pad + rows_per_block - 1) / rows_per_block, 2 * pr.heads, pr.batch);
+    if (bf16) {
+      if (lanes == 8) bwd_preprocess_kernel<true, 8><<<grid, 256, 0, stream>>>(p);
+      else if (lanes == 16) bwd_preprocess_kernel<true, 16><<<grid, 256, 0, stream>>>(p);
+      else bwd_preprocess_kernel<true, 32><<<grid, 256, 0, stream>>>(p);
+    } else {
+      if (lanes == 8) bwd_preprocess_kernel<false, 8><<<grid, 256, 0, stream>>>(p);
+      else if (lanes == 16) bwd_preprocess_kernel<false, 16><<<grid, 256, 0, stream>>>(p);
+      else bwd_preprocess_kernel<false, 32><<<grid, 256, 0, stream>>>(p);
+    }
+    FDA_CUDA_TRY(cudaGetLastError());
+  }
+  if (d_round == 64) return dispatch_bwd<64, 3, 6>(p, sm_count, bf16, softcap, stream);
+  return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stream);
+}
+
 int read_status_bwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};
   FDA_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_fda_status, sizeof(int) * 4));
   FDA_CUDA_TRY(cudaMemcpyToSymbol(g_fda_status, zero, sizeof(int) * 4));
   return FDA_OK;
 }
+
 }  // namespace fda

@@ -85,6 +85,11 @@ def _problem(q, k, batch, seqlen, total, block_size, softmax_scale, softcap, sm_
         cu_seqlens.data_ptr() if cu_seqlens is not None else None)
 
 
+def _padded_half(seqlen: int) -> int:
+    """Rows per half in the backward's statistics layout: the half length rounded up to the 128-row tile."""
+    return (max(seqlen // 2, 1) + 127) // 128 * 128
+
+
 def _stream_ptr(device):
     return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -206,11 +211,10 @@ def _diffusion_attn_backward(
         raise RuntimeError("softmax_lse must be contiguous")
     if softmax_scale is None:
         softmax_scale = head_dim ** (-0.5)
-    # per-row statistics, same layout as the LSE; returned like the reference's softmax_d
-    softmax_d = torch.empty(softmax_lse.shape, dtype=torch.float32, device=q.device)
+    n_pad = _padded_half(seqlen)
     if total == 0 or heads == 0:
-        dq.zero_(); dk.zero_(); dv.zero_(); softmax_d.zero_()
-        return softmax_d
+        dq.zero_(); dk.zero_(); dv.zero_()
+        return torch.zeros((batch, heads, 2, n_pad), dtype=torch.float32, device=q.device)
     lib = _lib.load()
     args = _lib.FdaBwdArgs()
     args.p = _problem(q, k, batch, seqlen, total, block_size, softmax_scale, softcap, sm_margin, deterministic,
@@ -224,9 +228,9 @@ def _diffusion_attn_backward(
     args.workspace_bytes = ws_bytes
     with torch.cuda.device(q.device):
         _lib.check(lib.fda_bwd(C.byref(args), _stream_ptr(q.device)))
-    # the first numel(lse) floats of the workspace hold rowsum(dO * O)
-    softmax_d.copy_(workspace[: softmax_d.numel() * 4].view(torch.float32).view(softmax_d.shape))
-    return softmax_d
+    # the workspace starts with rowsum(dO * O) in the padded (batch, heads, half, n_pad) layout; it plays the
+    # part of the reference's softmax_d return value (whose shape there depends on the sm90 tile sizes)
+    return workspace[: batch * heads * 2 * n_pad * 4].view(torch.float32).view(batch, heads, 2, n_pad)
 
 
 @torch.library.register_fake("fda::_diffusion_attn_backward")
@@ -248,7 +252,11 @@ def _diffusion_attn_backward_fake(
     deterministic: bool = False,
     sm_margin: int = 0,
 ) -> torch.Tensor:
-    return torch.empty(softmax_lse.shape, dtype=torch.float32, device=q.device)
+    if cu_seqlens is not None:
+        batch, seqlen = cu_seqlens.shape[0] - 1, int(max_seqlen)
+    else:
+        batch, seqlen = q.shape[0], q.shape[1]
+    return torch.empty((batch, q.shape[-2], 2, _padded_half(seqlen)), dtype=torch.float32, device=q.device)
 
 
 class _DiffusionAttention(torch.autograd.Function):

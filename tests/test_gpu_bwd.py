@@ -1,0 +1,132 @@
+"""Backward parity on the GPU through the public API (autograd -> C ABI) against the oracle's explicit
+gradients. Tolerance, as in the reference's tests (tests/test_diffusion_attn.py:76-104 there): for dq, dk, dv
+max|got - truth| <= 2 * max|plain - truth| + a few ulps, with truth = float32 oracle on the same inputs and
+plain = the oracle evaluated in the input precision. Also: bitwise reproducibility, packed == batched."""
+
+import pytest
+import torch
+
+from _util import assert_within_2x
+from fast_diffusion_attention import _lib, diffusion_attn_func, diffusion_attn_varlen_func
+from oracle import diffusion_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+SHAPES = [(2, 128, 4), (1, 256, 32), (3, 100, 3), (2, 333, 16), (1, 517, 7), (1, 64, 64), (1, 300, 128),
+          (2, 191, 200), (1, 1, 1), (2, 5, 2), (1, 1024, 1), (1, 777, 64), (1, 512, 256), (1, 640, 128)]
+
+
+def check_backward(q, k, v, bs, softcap=0.0, cu=None, deterministic=False):
+    g = torch.randn_like(q)
+    q, k, v = (t.detach().requires_grad_() for t in (q, k, v))
+    if cu is None:
+        out = diffusion_attn_func(q, k, v, bs, softcap=softcap, deterministic=deterministic)
+        truth = orc.backward(q.detach(), k.detach(), v.detach(), g, bs, softcap=softcap)
+        plain = orc.backward(q.detach(), k.detach(), v.detach(), g, bs, softcap=softcap, compute_dtype=q.dtype)
+    else:
+        ms = int((cu[1:] - cu[:-1]).max().item())
+        out = diffusion_attn_varlen_func(q, k, v, cu, cu, ms, ms, bs, softcap=softcap, deterministic=deterministic)
+        truth = orc.backward_varlen(q.detach(), k.detach(), v.detach(), g, cu.tolist(), bs, softcap=softcap)
+        plain = orc.backward_varlen(q.detach(), k.detach(), v.detach(), g, cu.tolist(), bs, softcap=softcap,
+                                    compute_dtype=q.dtype)
+    grads = torch.autograd.grad(out, (q, k, v), g)
+    assert _lib.device_status()[0] == 0
+    for name, got, t, pl in zip(("dq", "dk", "dv"), grads, truth, plain):
+        assert not torch.isnan(got.float()).any(), name
+        assert_within_2x(name, got, t, pl)
+    return grads
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("heads,heads_k", [(4, 4), (6, 2), (4, 1)])
+@pytest.mark.parametrize("batch,n,bs", SHAPES)
+def test_backward_bf16(batch, n, bs, heads, heads_k, d):
+    torch.manual_seed(n * 1000 + bs)
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    check_backward(q, k, v, bs)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("batch,n,bs", [(2, 333, 16), (1, 300, 128), (1, 777, 64)])
+def test_backward_fp16_softcap(batch, n, bs, d):
+    torch.manual_seed(n + bs)
+    q, k, v = (torch.randn(batch, 2 * n, h, d, device=DEV, dtype=torch.float16) for h in (4, 2, 2))
+    check_backward(q, k, v, bs, softcap=15.0)
+    check_backward(q, k, v, bs)
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("deterministic", [False, True])
+@pytest.mark.parametrize("bs", [1, 4, 13, 64, 160])
+def test_backward_varlen(bs, deterministic, d):
+    torch.manual_seed(bs)
+    ns = [17, 300, 1, 128, 513, 64, 2, 255, 0]
+    cu = torch.tensor([0] + list(torch.tensor([2 * x for x in ns]).cumsum(0)), device=DEV, dtype=torch.int32)
+    total = 2 * sum(ns)
+    q = torch.randn(total, 6, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(total, 2, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(total, 2, d, device=DEV, dtype=torch.bfloat16)
+    check_backward(q, k, v, bs, cu=cu, deterministic=deterministic)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_packed_equals_batched_bitwise(d):
+    """Packing equal-length samples gives exactly the batched result (out, lse and all gradients)."""
+    torch.manual_seed(0)
+    batch, n, heads, heads_k, bs = 3, 200, 4, 2, 8
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn_like(q)
+    out, lse = diffusion_attn_func(q, k, v, bs, deterministic=True, return_attn_probs=True)
+    grads = torch.autograd.grad(out, (q, k, v), g)
+    cu = torch.arange(0, batch * 2 * n + 1, 2 * n, device=DEV, dtype=torch.int32)
+    qv, kv, vv = [x.detach().reshape(-1, *x.shape[2:]).requires_grad_() for x in (q, k, v)]
+    out_v, lse_v = diffusion_attn_varlen_func(qv, kv, vv, cu, cu, 2 * n, 2 * n, bs, deterministic=True,
+                                              return_attn_probs=True)
+    grads_v = torch.autograd.grad(out_v, (qv, kv, vv), g.reshape(-1, *g.shape[2:]))
+    assert torch.equal(out.reshape(-1, *out.shape[2:]), out_v)
+    assert torch.equal(lse.permute(1, 0, 2).reshape(heads, -1), lse_v)
+    for x, y in zip(grads, grads_v):
+        assert torch.equal(x.reshape(-1, *x.shape[2:]), y)
+
+
+@pytest.mark.parametrize("heads,heads_k", [(4, 4), (8, 2)])
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_backward_bitwise_reproducible(heads, heads_k, deterministic):
+    torch.manual_seed(1)
+    batch, n, bs, d = 2, 700, 4, 128
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn_like(q)
+
+    def run():
+        out = diffusion_attn_func(q, k, v, bs, deterministic=deterministic)
+        return torch.autograd.grad(out, (q, k, v), g)
+
+    ref = run()
+    for _ in range(4):
+        for x, y in zip(run(), ref):
+            assert torch.equal(x, y)
+
+
+def test_backward_matches_golden_fixture():
+    """Gradients of the bf16 golden case produced by the reference's reference.py + autograd (tests/golden)."""
+    from _util import load_golden, make_inputs
+    from golden.make_golden import DENSE_CASES
+    name = "bf16_gqa"
+    B, n, H, Hk, d, bs, cap, scale, dt = DENSE_CASES[name]
+    gold = load_golden("attention_golden.npz")
+    q, k, v, do = make_inputs(int(gold[f"{name}/seed"]), (B, 2 * n, H, d), (B, 2 * n, Hk, d), torch.bfloat16, DEV)
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    out = diffusion_attn_func(q, k, v, bs)
+    grads = torch.autograd.grad(out, (q, k, v), do)
+    plain = orc.backward(q.detach(), k.detach(), v.detach(), do, bs, compute_dtype=torch.bfloat16)
+    for key, got, pl in zip(("dq", "dk", "dv"), grads, plain):
+        truth = torch.from_numpy(gold[f"{name}/{key}"]).to(DEV)
+        # the golden gradients were taken through a bf16-rounded forward output; allow that rounding too
+        assert_within_2x(key, got, truth, pl, atol=3e-2)
