@@ -1,0 +1,316 @@
+"""Benchmark of the block-diffusion attention training step (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): forward + backward of `diffusion_attn_func` on the BF16 MHA configuration the headline
+metric is quoted on: B=8 samples per GPU, n=2048 (2n=4096 rows), 16 heads, head_dim 128, block_size 256,
+q, k, v, dO ~ N(0,1) from a seed, cast to bf16 (synthetic stand-in: the reference benchmarks on seeded randn too,
+benchmarks/benchmark_diffusion.py there). Every rank owns its own B=8 shard (batch x head units are independent:
+no collective in the data path), so scaling is weak; torch.distributed is used only for the barrier and the
+max-over-ranks of the device time.
+
+Metric: training-step TFLOPS on visible (query, key) pairs: 3.5 * 4 * pairs * d * H per sample
+(forward 4*pairs*d*H, backward 2.5x; benchmarks/benchmark_diffusion.py:175-180 of the reference).
+
+The JSON line carries:
+  value      device-resident inputs, CUDA-event time of K steps (max over ranks), aggregate over ranks
+  e2e        same step through the public API with HOST (pinned) buffers: q, k, v, dO copied host->device and
+             out, dq, dk, dv copied device->host inside the timed region
+  roofline   the kernel with the largest share of the step, timed live with CUDA events between the launches
+  cpu_baseline   the CPU oracle (oracle/diffusion_oracle.py, a port of the reference's reference.py) on a bounded
+             sample of the same workload, on this box's host cores (rank 0, N=1 only)
+`--impl reference` times only that CPU implementation (all host threads) and prints the same line shape.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "fast-diffusion-attention_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOAD = dict(name="C2 bf16 MHA fwd+bwd", batch=8, n=2048, heads=16, heads_k=16, head_dim=128, block_size=256)
+METRIC = "train-step TFLOPS (visible pairs), bf16 d=128"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(source="measured", hbm_gbs=d["hbm_gbs"], tflops_burst=d["bf16_tflops"],
+                    tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [x.strip() for x in out.stdout.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
+        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [nm for i, nm in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return dict(sm_mhz=statistics.median(mhz) if mhz else None,
+                    sm_max_mhz=float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
+                    reasons=reasons, samples=len(self.samples))
+
+
+def make_cpu_sample(threads=None):
+    """The bounded CPU sample of the workload: ONE sample x 2 heads of the C2 shape (same n, head_dim,
+    block_size), float32 forward + explicit backward with the oracle. Returns (run_once, flops, description)."""
+    from oracle import diffusion_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    w = WORKLOAD
+    heads_sample = 2
+    g = torch.Generator().manual_seed(0)
+    shape = (1, 2 * w["n"], heads_sample, w["head_dim"])
+    q, k, v, do = (torch.randn(shape, generator=g).to(torch.bfloat16) for _ in range(4))
+    fwd, bwd = orc.step_flops([w["n"]], w["block_size"], heads_sample, w["head_dim"])
+
+    def run_once():
+        t0 = time.perf_counter()
+        orc.forward(q, k, v, w["block_size"])
+        orc.backward(q, k, v, do, w["block_size"])
+        return time.perf_counter() - t0
+
+    desc = (f"1 sample x {heads_sample} heads of the C2 shape (n={w['n']}, d={w['head_dim']}, "
+            f"block_size={w['block_size']}), float32 forward + explicit backward")
+    return run_once, fwd + bwd, desc
+
+
+def cpu_reference_run(seconds_budget=20.0):
+    run_once, flops, desc = make_cpu_sample()
+    run_once()  # warm-up (allocator, thread pool)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_start < seconds_budget and len(times) < 20):
+        times.append(run_once())
+    sec = statistics.median(times)
+    return dict(value=flops / sec / 1e12, unit="TFLOPS", cores=torch.get_num_threads(), kind="port",
+                sample=f"{desc}, median of {len(times)} runs, {sec:.2f} s each")
+
+
+def run_reference_arm(args, rank, world):
+    """The reference's CPU implementation of the path (its reference.py, restated in oracle/) on the host cores."""
+    if rank != 0:
+        return
+    run_once, flops, desc = make_cpu_sample()
+    for _ in range(max(args.warmup, 0)):
+        run_once()
+    times = [run_once() for _ in range(max(args.steps, 1))]
+    sec = statistics.mean(times)
+    value = flops / sec / 1e12
+    cores = torch.get_num_threads()
+    line = dict(impl="reference", metric=METRIC, value=value, unit="TFLOPS", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="f32", data="synthetic",
+                config=dict(workload=WORKLOAD["name"] + " (CPU: each step is a bounded sample)", **{
+                    k: v for k, v in WORKLOAD.items() if k != "name"}),
+                cpu_baseline=dict(value=value, unit="TFLOPS", cores=cores, kind="port", sample=desc + " per step"),
+                e2e=dict(value=value, unit="TFLOPS", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from fast_diffusion_attention import diffusion_attn_func, _lib
+    from fast_diffusion_attention.interface import _diffusion_attn_forward, backward_launch
+    from oracle import diffusion_oracle as orc
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    w = WORKLOAD
+    B, n, H, Hk, d, bs = w["batch"], w["n"], w["heads"], w["heads_k"], w["head_dim"], w["block_size"]
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host = [torch.randn(B, 2 * n, h, d, generator=gen).to(torch.bfloat16).pin_memory() for h in (H, Hk, Hk, H)]
+    q, k, v, do = (t.to(dev) for t in host)
+    fwd_flops, bwd_flops = orc.step_flops([n] * B, bs, H, d)
+    step_flops = fwd_flops + bwd_flops
+    scale = d ** -0.5
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws = torch.empty(_lib.load().fda_bwd_workspace_bytes(
+        __import__("ctypes").byref(_lib.FdaProblem(0, B, 2 * n, B * 2 * n, H, Hk, d, bs, scale, 0.0, 0, 0, None))),
+        dtype=torch.uint8, device=dev)
+
+    def step_device(events=None):
+        """One training step of the hot path with device-resident inputs, stage by stage (4 kernels)."""
+        if events is not None:
+            events[0].record()
+        out, lse = _diffusion_attn_forward(q, k, v, bs, None, None, None, None, None, scale, 0.0, 0)
+        if events is not None:
+            events[1].record()
+        backward_launch(do, q, k, v, out, lse, dq, dk, dv, bs, softmax_scale=scale, workspace=ws, stages=1)
+        if events is not None:
+            events[2].record()
+        backward_launch(do, q, k, v, out, lse, dq, dk, dv, bs, softmax_scale=scale, workspace=ws, stages=2)
+        if events is not None:
+            events[3].record()
+        backward_launch(do, q, k, v, out, lse, dq, dk, dv, bs, softmax_scale=scale, workspace=ws, stages=4)
+        if events is not None:
+            events[4].record()
+        return out
+
+    for _ in range(args.warmup):
+        step_device()
+    barrier()
+    status = _lib.device_status()
+    if status[0] != 0:
+        raise SystemExit(f"device-side wait expired during warm-up: {status}")
+
+    # ---- timed region: K steps, CUDA events on the launching (current) stream --------------------------------------
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e_start.record()
+        for i in range(args.steps):
+            step_device(ev[i])
+        e_end.record()
+        barrier()
+    total_ms = e_start.elapsed_time(e_end)
+    ms_t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_per_step = ms_t.item() / args.steps
+    value = step_flops * world / (ms_per_step * 1e-3) / 1e12
+
+    names = ["fwd_kernel", "bwd_preprocess_kernel", "bwd_dkdv_kernel", "bwd_dq_kernel"]
+    kernel_ms = [statistics.mean(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(args.steps)) for j in range(4)]
+    pairs_flops = fwd_flops / 4.0  # pairs * d * H summed over the batch
+    algorithmic = [4 * pairs_flops, 0.0, 8 * pairs_flops, 2 * pairs_flops]  # S,dP,dV,dK in dkdv; only dQ is new in dq
+    top = max(range(4), key=lambda j: kernel_ms[j])
+    peaks = measured_peaks()
+    achieved = algorithmic[top] / (kernel_ms[top] * 1e-3) / 1e12
+    roofline = dict(bound="tensor", kernel=names[top], achieved=achieved, peak=peaks["tflops_sustained"],
+                    unit="TFLOP/s", frac=achieved / peaks["tflops_sustained"], traffic=None,
+                    peak_source=peaks["source"] + " cuBLAS bf16, sustained (kernel timed inside a long step)",
+                    kernel_ms={nm: round(ms, 4) for nm, ms in zip(names, kernel_ms)},
+                    kernel_tflops_algorithmic={nm: (round(f / (ms * 1e-3) / 1e12, 1) if f else None)
+                                               for nm, f, ms in zip(names, algorithmic, kernel_ms)})
+
+    # ---- end to end through the public API with host buffers ---------------------------------------------------------
+    e2e = None
+    if not args.skip_e2e:
+        outs_host = [torch.empty_like(t).pin_memory() for t in (host[0], host[0], host[1], host[2])]
+        dev_in = [torch.empty_like(t, device=dev) for t in host]
+
+        def step_e2e():
+            for dst, src in zip(dev_in, host):
+                dst.copy_(src, non_blocking=True)
+            qd, kd, vd, dod = dev_in
+            qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+            out = diffusion_attn_func(qd, kd, vd, bs)
+            gq, gk, gv = torch.autograd.grad(out, (qd, kd, vd), dod)
+            for dst, src in zip(outs_host, (out.detach(), gq, gk, gv)):
+                dst.copy_(src, non_blocking=True)
+            qd.requires_grad_(False); kd.requires_grad_(False); vd.requires_grad_(False)
+
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        e2e_steps = max(3, min(args.steps, 10))
+        e_start.record()
+        for _ in range(e2e_steps):
+            step_e2e()
+        e_end.record()
+        barrier()
+        t = torch.tensor([e_start.elapsed_time(e_end)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item() / e2e_steps
+        e2e = dict(value=step_flops * world / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS",
+                   h2d_bytes_per_step=sum(t.numel() * 2 for t in host),
+                   d2h_bytes_per_step=sum(t.numel() * 2 for t in outs_host), ms_per_step=e2e_ms)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        cpu = cpu_reference_run()
+
+    if rank == 0:
+        line = dict(metric=METRIC, value=value, unit="TFLOPS", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=ms_per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    data="synthetic",
+                    config=dict(workload=w["name"], batch_per_gpu=B, n=n, seq_len=2 * n, heads=H, heads_k=Hk,
+                                head_dim=d, block_size=bs, global_batch=B * world, sharding="batch over ranks",
+                                l2="inputs+outputs per step ~1.1 GB, larger than the 126 MB L2"),
+                    per_gpu_tflops=value / world,
+                    frac_of_peak=dict(measured_burst=value / world / peaks["tflops_burst"],
+                                      measured_sustained=value / world / peaks["tflops_sustained"],
+                                      nominal_dense_bf16=value / world / 2250.0),
+                    clocks=clocks.summary(), e2e=e2e, gpu_launches=4 * args.steps, roofline=roofline,
+                    cpu_baseline=cpu)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -49,7 +49,7 @@ int fda_fwd(const FdaFwdArgs* a, void* stream) {
   return fda::launch_fwd(*a, static_cast<cudaStream_t>(stream));
 }
 
-int fda_bwd(const FdaBwdArgs* a, void* stream) {
+int fda_bwd_stages(const FdaBwdArgs* a, unsigned stage_mask, void* stream) {
   if (!a) return FDA_ERR_NULL;
   int rc = fda::check_problem(a->p, true);
   if (rc) return rc;
@@ -60,8 +60,10 @@ int fda_bwd(const FdaBwdArgs* a, void* stream) {
   }
   if (!a->workspace || a->workspace_bytes < fda::bwd_workspace_bytes(a->p)) return FDA_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(a->workspace) & 255) != 0) return FDA_ERR_WORKSPACE;
-  return fda::launch_bwd(*a, static_cast<cudaStream_t>(stream));
+  return fda::launch_bwd(*a, static_cast<cudaStream_t>(stream), stage_mask);
 }
+
+int fda_bwd(const FdaBwdArgs* a, void* stream) { return fda_bwd_stages(a, 7u, stream); }
 
 const char* fda_strerror(int status) {
   switch (status) {

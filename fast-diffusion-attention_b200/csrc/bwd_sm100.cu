@@ -745,8 +745,8 @@ int set_smem(Kernel kernel, int bytes, bool* done) {
 }
 
 template <int kHeadDim, int kStagesKv, int kStagesQ, bool kBf16, bool kSoftcap>
-int launch_bwd_instance(const BwdParams& p, int sm_count, cudaStream_t stream) {
-  {
+int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaStream_t stream) {
+  if (stages & 2u) {
     using Cfg = DkdvCfg<kHeadDim, kStagesKv>;
     auto kernel = bwd_dkdv_kernel<kHeadDim, kStagesKv, kBf16, kSoftcap>;
     static bool done[16] = {false};
@@ -757,7 +757,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, cudaStream_t stream) {
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
-  {
+  if (stages & 4u) {
     using Cfg = DqCfg<kHeadDim, kStagesQ>;
     auto kernel = bwd_dq_kernel<kHeadDim, kStagesQ, kBf16, kSoftcap>;
     static bool done[16] = {false};
@@ -772,13 +772,13 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, cudaStream_t stream) {
 }
 
 template <int kHeadDim, int kStagesKv, int kStagesQ>
-int dispatch_bwd(const BwdParams& p, int sm_count, bool bf16, bool softcap, cudaStream_t stream) {
+int dispatch_bwd(const BwdParams& p, int sm_count, bool bf16, bool softcap, unsigned stages, cudaStream_t stream) {
   if (bf16) {
-    return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, true>(p, sm_count, stream)
-                   : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, false>(p, sm_count, stream);
+    return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, true>(p, sm_count, stages, stream)
+                   : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, true, false>(p, sm_count, stages, stream);
   }
-  return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, true>(p, sm_count, stream)
-                 : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, false>(p, sm_count, stream);
+  return softcap ? launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, true>(p, sm_count, stages, stream)
+                 : launch_bwd_instance<kHeadDim, kStagesKv, kStagesQ, false, false>(p, sm_count, stages, stream);
 }
 
 inline int64_t round_up64(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
@@ -792,7 +792,7 @@ size_t bwd_workspace_bytes(const FdaProblem& pr) {
   return static_cast<size_t>(2 * one + 256);
 }
 
-int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream) {
+int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   const FdaProblem& pr = a.p;
   DeviceInfo info;
   int rc = current_device_info(&info);
@@ -870,7 +870,7 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream) {
   if (sm_count < 1) sm_count = 1;
   const bool bf16 = pr.dtype == FDA_BF16;
 
-  {
+  if (stage_mask & 1u) {
     const int lanes = d <= 64 ? 8 : (d <= 128 ? 16 : 32);
     const int rows_per_block = 8 * (32 / lanes);
     dim3 grid((p.n_pad + rows_per_block - 1) / rows_per_block, 2 * pr.heads, pr.batch);
@@ -885,8 +885,8 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream) {
     }
     FDA_CUDA_TRY(cudaGetLastError());
   }
-  if (d_round == 64) return dispatch_bwd<64, 3, 6>(p, sm_count, bf16, softcap, stream);
-  return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stream);
+  if (d_round == 64) return dispatch_bwd<64, 3, 6>(p, sm_count, bf16, softcap, stage_mask, stream);
+  return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
 int read_status_bwd(int32_t* out4) {

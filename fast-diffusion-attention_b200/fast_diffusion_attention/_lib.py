@@ -44,7 +44,7 @@ class FdaBwdArgs(C.Structure):
 
 
 EXPORTS = [
-    "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_strerror",
+    "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_bwd_stages", "fda_strerror",
     "fda_last_cuda_error", "fda_device_status", "fda_version", "fda_geom_key_plan", "fda_geom_query_plan",
     "fda_geom_classify", "fda_selftest_umma",
 ]
@@ -70,6 +70,8 @@ def load():
     lib.fda_fwd.argtypes = [C.POINTER(FdaFwdArgs), C.c_void_p]
     lib.fda_bwd.restype = C.c_int
     lib.fda_bwd.argtypes = [C.POINTER(FdaBwdArgs), C.c_void_p]
+    lib.fda_bwd_stages.restype = C.c_int
+    lib.fda_bwd_stages.argtypes = [C.POINTER(FdaBwdArgs), C.c_uint, C.c_void_p]
     lib.fda_strerror.restype = C.c_char_p
     lib.fda_strerror.argtypes = [C.c_int]
     lib.fda_last_cuda_error.restype = C.c_char_p

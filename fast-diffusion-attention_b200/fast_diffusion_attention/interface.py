@@ -177,25 +177,11 @@ def _diffusion_attn_forward_fake(
     return out, lse
 
 
-@torch.library.custom_op("fda::_diffusion_attn_backward", mutates_args=("dq", "dk", "dv"), device_types="cuda")
-def _diffusion_attn_backward(
-    dout: torch.Tensor,
-    q: torch.Tensor,
-    k: torch.Tensor,
-    v: torch.Tensor,
-    out: torch.Tensor,
-    softmax_lse: torch.Tensor,
-    dq: torch.Tensor,
-    dk: torch.Tensor,
-    dv: torch.Tensor,
-    block_size: int,
-    cu_seqlens: Optional[torch.Tensor] = None,
-    max_seqlen: Optional[int] = None,
-    softmax_scale: Optional[float] = None,
-    softcap: float = 0.0,
-    deterministic: bool = False,
-    sm_margin: int = 0,
-) -> torch.Tensor:
+def backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_seqlens=None, max_seqlen=None,
+                    softmax_scale=None, softcap=0.0, deterministic=False, sm_margin=0, workspace=None, stages=7):
+    """Validate, size the workspace and enqueue the backward stages selected by `stages` (bit 0 preprocess,
+    bit 1 dK/dV, bit 2 dQ; 7 = the whole backward) on the current stream. A caller that times or profiles single
+    stages passes the same `workspace` to every call. Returns the (batch, heads, 2, n_pad) view of rowsum(dO*O)."""
     dout, q, k, v, out = [maybe_contiguous(x) for x in (dout, q, k, v, out)]
     batch, seqlen, total = _check_inputs(q, k, v, cu_seqlens, max_seqlen, block_size, backward=True)
     varlen = cu_seqlens is not None
@@ -223,14 +209,42 @@ def _diffusion_attn_backward(
         _tensor_view(t, varlen) for t in (q, k, v, out, dout, dq, dk, dv))
     args.lse = softmax_lse.data_ptr()
     ws_bytes = lib.fda_bwd_workspace_bytes(C.byref(args.p))
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    if workspace is None:
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    elif workspace.numel() < ws_bytes or workspace.dtype != torch.uint8:
+        raise RuntimeError("workspace must be a uint8 CUDA tensor of at least fda_bwd_workspace_bytes bytes")
     args.workspace = workspace.data_ptr()
     args.workspace_bytes = ws_bytes
     with torch.cuda.device(q.device):
-        _lib.check(lib.fda_bwd(C.byref(args), _stream_ptr(q.device)))
+        _lib.check(lib.fda_bwd_stages(C.byref(args), int(stages), _stream_ptr(q.device)))
     # the workspace starts with rowsum(dO * O) in the padded (batch, heads, half, n_pad) layout; it plays the
     # part of the reference's softmax_d return value (whose shape there depends on the sm90 tile sizes)
     return workspace[: batch * heads * 2 * n_pad * 4].view(torch.float32).view(batch, heads, 2, n_pad)
+
+
+
+
+@torch.library.custom_op("fda::_diffusion_attn_backward", mutates_args=("dq", "dk", "dv"), device_types="cuda")
+def _diffusion_attn_backward(
+    dout: torch.Tensor,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    out: torch.Tensor,
+    softmax_lse: torch.Tensor,
+    dq: torch.Tensor,
+    dk: torch.Tensor,
+    dv: torch.Tensor,
+    block_size: int,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    max_seqlen: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+    softcap: float = 0.0,
+    deterministic: bool = False,
+    sm_margin: int = 0,
+) -> torch.Tensor:
+    return backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_seqlens, max_seqlen,
+                           softmax_scale, softcap, deterministic, sm_margin)
 
 
 @torch.library.register_fake("fda::_diffusion_attn_backward")

@@ -106,6 +106,12 @@ size_t fda_bwd_workspace_bytes(const FdaProblem* p);
 int fda_fwd(const FdaFwdArgs* args, void* stream);
 int fda_bwd(const FdaBwdArgs* args, void* stream);
 
+/* Same as fda_bwd but runs only the stages selected by `stage_mask`, in order, on `stream`: bit 0 the
+ * preprocess (delta and LSE*log2e into the workspace), bit 1 the dK/dV kernel, bit 2 the dQ kernel. Later
+ * stages read what the preprocess left in the workspace. For profiling and per-kernel timing; the reference
+ * has the same stages as separate launches (csrc/fda/flash_bwd_launch_template.h:47-239). */
+int fda_bwd_stages(const FdaBwdArgs* args, unsigned stage_mask, void* stream);
+
 /* Message for a status code. */
 const char* fda_strerror(int status);
 /* Last CUDA error string seen by this thread inside the library ("" if none). */
