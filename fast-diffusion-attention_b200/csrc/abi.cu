@@ -135,7 +135,16 @@ int fda_geom_query_plan(int kh, int k0, int k1, int n, int bs, int bm, int32_t* 
 }
 
 int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int bs, int bm, int need_full_rows) {
-  return fda::classify_tile(qh, kh, qa, qb, k0, bn, n, bs, bm, need_full_rows != 0);
+  (void)bm;
+  if (need_full_rows == 0) {
+    // query-tile-stationary form used by the forward and dQ kernels
+    return fda::key_span(qh, kh, qa, qb, n, bs).classify(k0, bn);
+  }
+  // key-tile-stationary form used by the dK/dV kernel: a key tile that runs past n is never "full"
+  const int k1 = fda::imin(k0 + bn, n);
+  int c = fda::query_span(qh, kh, k0, k1, n, bs).classify(qa, qb - qa);
+  if (c == fda::kTileFull && k1 - k0 < bn) c = fda::kTileMasked;
+  return c;
 }
 
 int fda_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, void* stream) {

@@ -25,6 +25,7 @@
 #include "geometry.h"
 #include "host_util.h"
 #include "ptx.cuh"
+#include "sched.cuh"
 
 namespace fda {
 namespace {
@@ -51,6 +52,8 @@ struct BwdParams {
   int batch, seqlen, total, heads, heads_k, head_dim, block_size;
   int n_pad;           // round_up(max n, 128)
   int tiles_per_half;  // n_pad / 128
+  int* ticket_kv;      // work counters of the two persistent kernels, zeroed before each launch
+  int* ticket_q;
   float scale_log2, softcap_pre, softmax_scale;
 };
 
@@ -243,12 +246,15 @@ struct KvItem {
 };
 
 __device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
+  // (sample, KV head)-major: the CTAs running at the same time stream the Q / dO tiles of a few heads, which then
+  // stay in L2. Inside a head: clean key tiles first, early ones first (they are seen by the most queries), then
+  // the noisy key tiles (one block of queries each) as filler.
   KvItem it;
-  const int per_tile = 2 * p.heads_k * p.batch;
-  const int kt = idx / per_tile;  // ascending: early clean key tiles are seen by the most queries
-  const int rem = idx - kt * per_tile;
-  it.kh = 1 - (rem & 1);          // clean first
-  const int bh = rem >> 1;
+  const int per_bh = 2 * p.tiles_per_half;
+  const int bh = idx / per_bh;
+  const int rem = idx - bh * per_bh;
+  it.kh = rem < p.tiles_per_half ? 1 : 0;
+  const int kt = rem < p.tiles_per_half ? rem : rem - p.tiles_per_half;
   it.b = bh / p.heads_k;
   it.hk = bh - it.b * p.heads_k;
   const Sample sm = sample_of(p, it.b);
@@ -261,11 +267,31 @@ __device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
   return it;
 }
 
+// Query spans of the item's key tile: [0] for query tiles of the same half, [1] for noisy query tiles seeing
+// clean keys. Built once per item; classifying a query tile is then compares only.
+struct KvSpans {
+  Span same, cross;
+  bool partial_keys;
+  __device__ __forceinline__ int classify(int qh, int kh, int qa, int qb) const {
+    int c = (qh == kh ? same : cross).classify(qa, qb - qa);
+    if (c == kTileFull && partial_keys) c = kTileMasked;
+    return c;
+  }
+};
+
+__device__ __forceinline__ KvSpans make_kv_spans(const KvItem& it, int bs) {
+  KvSpans sp;
+  sp.same = query_span(it.kh, it.kh, it.k0, it.k1, it.n, bs);
+  sp.cross = it.kh == 1 ? query_span(0, 1, it.k0, it.k1, it.n, bs) : Span{0, 0, 0, 0};
+  sp.partial_keys = (it.k1 - it.k0) < kTile;
+  return sp;
+}
+
 template <int kHeadDim, int kStages>
 struct DkdvCfg {
   using T = TileCfg<kHeadDim>;
   static constexpr int kStageBytes = 2 * T::kTileBytes + 1024;  // Q tile, dO tile, lse2[128], delta[128]
-  static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
   static constexpr int kThreads = 320;
   static constexpr int kTmemST = 0, kTmemDPT = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
   static_assert(256 + 2 * kHeadDim <= 512, "tensor memory budget");
@@ -290,10 +316,12 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
   uint64_t* acc_full = pds_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    sched_init(mbox, 9);
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -322,10 +350,13 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
     if (lane == 0) {
       uint32_t n_item = 0, slot = 0;
       bool alive = true;
-      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_produce(mbox, n_sched, p.ticket_kv, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
         const KvItem it = decode_kv_item(p, idx);
         if (!it.valid) continue;
         const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+        const KvSpans spans = make_kv_spans(it, bs);
         if (!ptx::mbar_wait(kv_empty, (n_item & 1) ^ 1, abort_flag, 41)) break;
         ptx::mbar_expect_tx(kv_full, 2 * T::kTileBytes);
         const int k_row = it.row0 + it.kh * it.n + it.k0;
@@ -337,7 +368,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
             int qh, qt;
             plan.step(s, it.kh, qh, qt);
             const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-            if (classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs) == kTileSkip) continue;
+            if (spans.classify(qh, it.kh, qa, qb) == kTileSkip) continue;
             const uint32_t stage = slot % kStages;
             if (!ptx::mbar_wait(&st_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 42)) { alive = false; break; }
             uint8_t* base = sStage + stage * Cfg::kStageBytes;
@@ -363,10 +394,13 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
       uint32_t n_item = 0, slot = 0, cnt = 0;
       bool alive = true;
-      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
         const KvItem it = decode_kv_item(p, idx);
         if (!it.valid) continue;
         const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+        const KvSpans spans = make_kv_spans(it, bs);
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
         bool acc = false;
         for (int g = 0; g < group && alive; ++g) {
@@ -374,7 +408,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
             int qh, qt;
             plan.step(s, it.kh, qh, qt);
             const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-            if (classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs) == kTileSkip) continue;
+            if (spans.classify(qh, it.kh, qa, qb) == kTileSkip) continue;
             const uint32_t stage = slot % kStages;
             if (!ptx::mbar_wait(&st_full[stage], (slot / kStages) & 1, abort_flag, 52)) { alive = false; break; }
             ptx::tc_fence_after();
@@ -407,25 +441,31 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t n_item = 0, slot = 0, cnt = 0;
     bool alive = true;
-    for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+    for (uint32_t n_sched = 0; alive; ++n_sched) {
+      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      if (idx < 0 || idx >= total_items) break;
       const KvItem it = decode_kv_item(p, idx);
       if (!it.valid) continue;
       const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
+      const KvSpans spans = make_kv_spans(it, bs);
       const int kj = it.k0 + row;
+      // queries that see this thread's key: same-half tiles and (clean keys only) noisy tiles of later blocks
+      int same_lo, same_hi, cross_lo, cross_hi;
+      query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
+      query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
       for (int g = 0; g < group && alive; ++g) {
         for (int s = 0; s < plan.steps(); ++s) {
           int qh, qt;
           plan.step(s, it.kh, qh, qt);
           const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-          const int cls = classify_tile(qh, it.kh, qa, qb, it.k0, kTile, it.n, bs);
+          const int cls = spans.classify(qh, it.kh, qa, qb);
           if (cls == kTileSkip) continue;
           const uint32_t stage = slot % kStages;
           ++slot;
           int lo = 0, hi = 0;
           if (cls == kTileMasked) {
-            query_interval(qh, it.kh, kj, it.n, bs, lo, hi);
-            lo -= qa + wg * 64;
-            hi -= qa + wg * 64;
+            lo = (qh == it.kh ? same_lo : cross_lo) - (qa + wg * 64);
+            hi = (qh == it.kh ? same_hi : cross_hi) - (qa + wg * 64);
           }
           const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * T::kTileBytes);
           // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
@@ -496,12 +536,13 @@ struct QItem {
 };
 
 __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
+  // (sample, head)-major for L2 reuse of K / V; inside a head late query tiles first (they see the most keys).
   QItem it;
-  const int per_tile = 2 * p.heads * p.batch;
-  const int t_rev = idx / per_tile;
-  const int rem = idx - t_rev * per_tile;
+  const int per_bh = 2 * p.tiles_per_half;
+  const int bh = idx / per_bh;
+  const int rem = idx - bh * per_bh;
   it.qh = rem & 1;
-  const int bh = rem >> 1;
+  const int t_rev = rem >> 1;
   it.b = bh / p.heads;
   it.h = bh - it.b * p.heads;
   it.hk = it.h / (p.heads / p.heads_k);
@@ -509,16 +550,28 @@ __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
   it.n = sm.n;
   it.row0 = sm.row0;
   it.bcoord = sm.bcoord;
-  it.qa = (p.tiles_per_half - 1 - t_rev) * kTile;  // late query tiles see the most keys: longest first
+  it.qa = (p.tiles_per_half - 1 - t_rev) * kTile;
   it.valid = it.qa < it.n;
   it.qb = imin(it.qa + kTile, it.n);
   return it;
 }
 
+struct QSpans {
+  Span half[2];  // key spans of the query tile per key half (0 noisy, 1 clean)
+  __device__ __forceinline__ int classify(int kh, int kt) const { return half[kh].classify(kt * kTile, kTile); }
+};
+
+__device__ __forceinline__ QSpans make_q_spans(const QItem& it, int bs) {
+  QSpans sp;
+  sp.half[0] = key_span(it.qh, 0, it.qa, it.qb, it.n, bs);
+  sp.half[1] = key_span(it.qh, 1, it.qa, it.qb, it.n, bs);
+  return sp;
+}
+
 template <int kHeadDim, int kStages>
 struct DqCfg {
   using T = TileCfg<kHeadDim>;
-  static constexpr int kSmemBytes = (2 + kStages) * T::kTileBytes + 1024 + 256;
+  static constexpr int kSmemBytes = (2 + kStages) * T::kTileBytes + 1024 + 512;
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDS = 256, kTmemDQ = 384;
   static_assert(384 + kHeadDim <= 512, "tensor memory budget");
 };
@@ -544,10 +597,12 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
   uint64_t* dq_full = ds_free + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    sched_init(mbox, 9);
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -576,10 +631,13 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
     if (lane == 0) {
       uint32_t n_item = 0, slot = 0;
       bool alive = true;
-      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_produce(mbox, n_sched, p.ticket_q, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
         const QItem it = decode_q_item(p, idx);
         if (!it.valid) continue;
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        const QSpans spans = make_q_spans(it, bs);
         if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 71)) break;
         ptx::mbar_expect_tx(q_full, 2 * T::kTileBytes);
         const int q_row = it.row0 + it.qh * it.n + it.qa;
@@ -588,7 +646,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
         for (int s = 0; s < plan.steps() && alive; ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
-          if (classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs) == kTileSkip) continue;
+          if (spans.classify(kh, kt) == kTileSkip) continue;
           const int k_row = it.row0 + kh * it.n + kt * kTile;
           for (int which = 0; which < 2; ++which) {
             const uint32_t stage = slot % kStages;
@@ -610,15 +668,18 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
       uint32_t n_item = 0, slot = 0, cnt_sdp = 0, cnt_ds = 0;
       bool alive = true;
-      for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
         const QItem it = decode_q_item(p, idx);
         if (!it.valid) continue;
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        const QSpans spans = make_q_spans(it, bs);
         int active = 0;
         for (int s = 0; s < plan.steps(); ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
-          active += classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs) != kTileSkip;
+          active += spans.classify(kh, kt) != kTileSkip;
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
         // S/dP of step j+1 are issued before dQ of step j so the tensor pipe has work during the softmax math
@@ -662,10 +723,13 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t n_item = 0, cnt = 0;
     bool alive = true;
-    for (int idx = blockIdx.x; idx < total_items && alive; idx += gridDim.x) {
+    for (uint32_t n_sched = 0; alive; ++n_sched) {
+      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      if (idx < 0 || idx >= total_items) break;
       const QItem it = decode_q_item(p, idx);
       if (!it.valid) continue;
       const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+      const QSpans spans = make_q_spans(it, bs);
       const int r = it.qa + row;
       const bool row_valid = r < it.n;
       const int r_eff = row_valid ? r : it.n - 1;
@@ -677,7 +741,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       for (int s = 0; s < plan.steps() && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
-        const int cls = classify_tile(it.qh, kh, it.qa, it.qb, kt * kTile, kTile, it.n, bs);
+        const int cls = spans.classify(kh, kt);
         if (cls == kTileSkip) continue;
         int lo = 0, hi = 0;
         if (cls == kTileMasked) {
@@ -857,6 +921,9 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * p.n_pad * 4, 256);
   p.delta_pad = static_cast<float*>(a.workspace);
   p.lse2_pad = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + one);
+  p.ticket_kv = reinterpret_cast<int*>(static_cast<uint8_t*>(a.workspace) + 2 * one);
+  p.ticket_q = p.ticket_kv + 32;
+  if (stage_mask & 6u) FDA_CUDA_TRY(cudaMemsetAsync(p.ticket_kv, 0, 256, stream));
   const bool softcap = pr.softcap > 0.f;
   p.softmax_scale = pr.softmax_scale;
   if (softcap) {

@@ -24,9 +24,16 @@
 #include "geometry.h"
 #include "host_util.h"
 #include "ptx.cuh"
+#include "sched.cuh"
 
 namespace fda {
 namespace {
+
+#ifdef FDA_PHASE_CLOCKS
+// Debug build only: cycles one softmax thread spends per phase, summed over CTAs (wait, load, math, store,
+// epilogue/other) and the number of tile steps.
+__device__ unsigned long long g_fda_phase[8];
+#endif
 
 constexpr int kBlockM = 128;  // query rows per tile (= tensor-memory lanes)
 constexpr int kBlockN = 128;  // keys per tile
@@ -43,6 +50,7 @@ struct FwdParams {
   int batch, seqlen, total, heads, heads_k, head_dim, block_size;
   int items_per_half;  // ceil(max n / rows per item)
   int total_items;
+  int* ticket;         // global work counter, zeroed before the launch
   float scale_log2;    // exponent scale: softmax_scale*log2(e), or softcap*log2(e) with softcapping
   float softcap_pre;   // softmax_scale / softcap (tanh argument scale)
   float lse_scale;     // natural-log scale of the row maximum: softmax_scale, or softcap
@@ -57,12 +65,14 @@ struct Item {
 
 template <int kQTiles>
 __device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
+  // (sample, head)-major so that the CTAs running at the same time share the K/V of a few heads in L2; inside a
+  // head the items with the most key tiles (late query rows) come first.
   Item it;
-  const int per_p = 2 * p.heads * p.batch;
-  const int p_rev = idx / per_p;
-  const int rem = idx - p_rev * per_p;
+  const int per_bh = 2 * p.items_per_half;
+  const int bh = idx / per_bh;
+  const int rem = idx - bh * per_bh;
   it.qh = rem & 1;
-  const int bh = rem >> 1;
+  const int p_rev = rem >> 1;
   it.b = bh / p.heads;
   it.h = bh - it.b * p.heads;
   it.hk = it.h / (p.heads / p.heads_k);
@@ -84,13 +94,26 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
   return it;
 }
 
-// Classification of key tile (kh, kt) for query tile t of the item (skip when the tile has no rows).
-template <int kQTiles>
-__device__ __forceinline__ int classify_for(const Item& it, int t, int kh, int kt, int bs) {
+// Key spans of query tile t of the item, one per key half (index 0 noisy, 1 clean). Built once per item (the
+// divisions by the block size happen here); classifying a key tile afterwards is a few compares. A query tile
+// without rows gets empty spans, so every key tile is "skip" for it.
+struct TileSpans {
+  Span half[2];
+  __device__ __forceinline__ int classify(int kh, int kt) const { return half[kh].classify(kt * kBlockN, kBlockN); }
+};
+
+__device__ __forceinline__ TileSpans make_tile_spans(const Item& it, int t, int bs) {
+  TileSpans ts;
   const int ta = it.qa + t * kBlockM;
-  if (ta >= it.qb) return kTileSkip;
+  if (ta >= it.qb) {
+    ts.half[0] = Span{0, 0, 0, 0};
+    ts.half[1] = Span{0, 0, 0, 0};
+    return ts;
+  }
   const int tb = imin(ta + kBlockM, it.qb);
-  return classify_tile(it.qh, kh, ta, tb, kt * kBlockN, kBlockN, it.n, bs);
+  ts.half[0] = key_span(it.qh, 0, ta, tb, it.n, bs);
+  ts.half[1] = key_span(it.qh, 1, ta, tb, it.n, bs);
+  return ts;
 }
 
 template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
@@ -124,12 +147,14 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
   uint64_t* o_full = p_full + kQTiles;           // kQTiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kQTiles);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    sched_init(mbox, 4 * kQTiles + 1);
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -163,7 +188,9 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
     if (lane == 0) {
       uint32_t slot = 0, n_item = 0;
       bool alive = true;
-      for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_produce(mbox, n_sched, p.ticket, abort_flag);
+        if (idx < 0 || idx >= p.total_items) break;
         const Item it = decode_item<kQTiles>(p, idx);
         if (!it.valid) continue;
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
@@ -235,11 +262,16 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         }
       };
 
-      for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= p.total_items) break;
         const Item it = decode_item<kQTiles>(p, idx);
         if (!it.valid) continue;
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
         const int steps = plan.steps();
+        TileSpans spans[kQTiles];
+#pragma unroll
+        for (int t = 0; t < kQTiles; ++t) spans[t] = make_tile_spans(it, t, bs);
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 21)) { alive = false; break; }
         bool pend[kQTiles], o_acc[kQTiles];
 #pragma unroll
@@ -266,7 +298,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
               o_acc[t] = true;
               pend[t] = false;
             }
-            if (s < steps && classify_for<kQTiles>(it, t, kh, kt, bs) != kTileSkip) {
+            if (s < steps && spans[t].classify(kh, kt) != kTileSkip) {
               issue_s(t, slot_k % kStages);
               ptx::umma_commit(&s_full[t]);
               pend[t] = true;
@@ -296,11 +328,21 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
     const uint32_t tmem_o = tmem + Cfg::kTmemO + t * kHeadDim + lane_addr;
     uint32_t cnt_s = 0, cnt_o = 0;
     bool alive = true;
-    for (int idx = blockIdx.x; idx < p.total_items && alive; idx += gridDim.x) {
+#ifdef FDA_PHASE_CLOCKS
+    long long ph_wait = 0, ph_ld = 0, ph_math = 0, ph_st = 0, ph_epi = 0, ph_steps = 0, ph_t = 0, ph_owait = 0, ph_pre = 0;
+#define FDA_PH(acc) do { const long long _n = clock64(); acc += _n - ph_t; ph_t = _n; } while (0)
+    ph_t = clock64();
+#else
+#define FDA_PH(acc) do {} while (0)
+#endif
+    for (uint32_t n_sched = 0; alive; ++n_sched) {
+      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      if (idx < 0 || idx >= p.total_items) break;
       const Item it = decode_item<kQTiles>(p, idx);
       if (!it.valid) continue;
       const int ta = it.qa + t * kBlockM;
       if (ta >= it.qb) continue;
+      const TileSpans spans = make_tile_spans(it, t, bs);
       const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
       const int steps = plan.steps();
       const int r = ta + row;                      // position in the half
@@ -314,9 +356,11 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       for (int s = 0; s < steps && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
-        const int cls = classify_for<kQTiles>(it, t, kh, kt, bs);
+        const int cls = spans.classify(kh, kt);
         if (cls == kTileSkip) continue;
+        FDA_PH(ph_pre);
         if (!ptx::mbar_wait(&s_full[t], cnt_s & 1, abort_flag, 31)) { alive = false; break; }
+        FDA_PH(ph_wait);
         ++cnt_s;
         ptx::tc_fence_after();
         float v[kBlockN];
@@ -326,6 +370,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
           for (int c = 0; c < kBlockN / 32; ++c) ptx::tmem_ld32(tmem_s + c * 32, u + c * 32);
           ptx::tmem_wait_ld();
         }
+        FDA_PH(ph_ld);
         if (kSoftcap) {
 #pragma unroll
           for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * p.softcap_pre);
@@ -376,16 +421,23 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
           pk[c / 2] = ptx::pack2<kBf16>(p0, p1);
         }
         l_run += sum;
+        FDA_PH(ph_math);
 #pragma unroll
         for (int c = 0; c < kBlockN / 64; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive(&p_full[t]);
         o_started = true;
+        FDA_PH(ph_st);
+#ifdef FDA_PHASE_CLOCKS
+        ++ph_steps;
+#endif
       }
       if (!alive) break;
       // ---- epilogue: O / l -> global, LSE
+      FDA_PH(ph_pre);
       if (!ptx::mbar_wait(&o_full[t], cnt_o & 1, abort_flag, 32)) { alive = false; break; }
+      FDA_PH(ph_owait);
       ++cnt_o;
       ptx::tc_fence_after();
       const float inv_l = 1.f / l_run;
@@ -423,13 +475,27 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         p.lse[li] = lse;
       }
       ptx::tc_fence_before();
+      FDA_PH(ph_epi);
     }
+#ifdef FDA_PHASE_CLOCKS
+    if (threadIdx.x == 0) {
+      atomicAdd(&g_fda_phase[6], (unsigned long long)ph_owait);
+      atomicAdd(&g_fda_phase[7], (unsigned long long)ph_pre);
+      atomicAdd(&g_fda_phase[0], (unsigned long long)ph_wait);
+      atomicAdd(&g_fda_phase[1], (unsigned long long)ph_ld);
+      atomicAdd(&g_fda_phase[2], (unsigned long long)ph_math);
+      atomicAdd(&g_fda_phase[3], (unsigned long long)ph_st);
+      atomicAdd(&g_fda_phase[4], (unsigned long long)ph_epi);
+      atomicAdd(&g_fda_phase[5], (unsigned long long)ph_steps);
+    }
+#endif
   }
 
   ptx::tc_fence_before();
   __syncthreads();
   if (warp == Cfg::kLoadWarp) ptx::tmem_dealloc(tmem, 512);
 }
+#undef FDA_PH
 
 template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
 int launch_fwd_instance(const FwdParams& p, int grid, cudaStream_t stream) {
@@ -513,6 +579,9 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
     p.lse_scale = pr.softmax_scale;
   }
   if (p.total_items <= 0) return FDA_OK;
+  if (!a.workspace || a.workspace_bytes < 256) return FDA_ERR_WORKSPACE;
+  p.ticket = static_cast<int*>(a.workspace);
+  FDA_CUDA_TRY(cudaMemsetAsync(p.ticket, 0, 256, stream));
   int grid = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
   if (grid < 1) grid = 1;
   if (grid > p.total_items) grid = p.total_items;
@@ -521,6 +590,15 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   if (d_round == 128) return dispatch_fwd<128, 2, 4>(p, grid, bf16, softcap, stream);
   return dispatch_fwd<256, 1, 2>(p, grid, bf16, softcap, stream);
 }
+
+#ifdef FDA_PHASE_CLOCKS
+extern "C" int fda_debug_phase_clocks(unsigned long long* out8) {
+  unsigned long long zero[8] = {0};
+  if (cudaMemcpyFromSymbol(out8, g_fda_phase, sizeof(zero)) != cudaSuccess) return 1;
+  if (cudaMemcpyToSymbol(g_fda_phase, zero, sizeof(zero)) != cudaSuccess) return 1;
+  return 0;
+}
+#endif
 
 int read_status_fwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};

@@ -66,6 +66,41 @@ FDA_HD int classify_tile(int qh, int kh, int qa, int qb, int k0, int bn, int n, 
   return kTileMasked;
 }
 
+// Division-free classification for the kernels' inner loops. A span holds the visibility intervals of the FIRST
+// and the LAST position of a fixed tile on one axis (queries for the forward / dQ kernels, keys for the dK/dV
+// kernel); it is built once per work item (that is where the divisions by the block size happen) and then
+// classifies any tile [x0, x0 + len) on the other axis with compares only. Both interval ends are monotone, so
+// the union over the fixed tile is [lo_first, hi_last) and the intersection is [lo_last, hi_first).
+struct Span {
+  int lo_first, hi_first, lo_last, hi_last;
+  // `limit` = number of valid positions on the other axis (n): a full tile must lie inside it.
+  FDA_HD int classify(int x0, int len) const {
+    const int x1 = x0 + len;
+    if (x0 >= hi_last || x1 <= lo_first || hi_last <= lo_first) return kTileSkip;
+    if (lo_last <= x0 && x1 <= hi_first) return kTileFull;
+    return kTileMasked;
+  }
+};
+
+// Keys of half kh seen by the query rows [qa, qb) of half qh (qa < qb <= n). classify(k0, bn) then agrees with
+// classify_tile(qh, kh, qa, qb, k0, bn, n, bs).
+FDA_HD Span key_span(int qh, int kh, int qa, int qb, int n, int bs) {
+  Span s;
+  key_interval(qh, kh, qa, n, bs, s.lo_first, s.hi_first);
+  key_interval(qh, kh, qb - 1, n, bs, s.lo_last, s.hi_last);
+  return s;
+}
+
+// Query rows of half qh that see the keys [k0, k1) of half kh (k0 < k1 <= n). classify(qa, rows) calls a query
+// tile full when all of its `rows` positions see every key of [k0, k1); the caller still has to treat a key
+// tile that runs past n (k1 - k0 < tile) as masked.
+FDA_HD Span query_span(int qh, int kh, int k0, int k1, int n, int bs) {
+  Span s;
+  query_interval(qh, kh, k0, n, bs, s.lo_first, s.hi_first);
+  query_interval(qh, kh, k1 - 1, n, bs, s.lo_last, s.hi_last);
+  return s;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Forward-shaped enumeration (also used by the dQ kernel): key tiles visited by the query rows [qa, qb) of
 // half qh. Steps 0..n_clean-1 are clean key tiles 0.., the remaining n_noisy steps are noisy key tiles

@@ -129,7 +129,9 @@ const char* fda_version(void);
 int fda_geom_key_plan(int qh, int qa, int qb, int n, int bs, int bn, int32_t* out_half, int32_t* out_tile, int cap);
 /* Query tiles visited by keys [k0, k1) of half kh. */
 int fda_geom_query_plan(int kh, int k0, int k1, int n, int bs, int bm, int32_t* out_half, int32_t* out_tile, int cap);
-/* 0 skip, 1 fully visible, 2 needs the element mask. */
+/* 0 skip, 1 fully visible, 2 needs the element mask. need_full_rows = 0 classifies with the query tile fixed
+ * (forward, dQ kernel); 1 with the key tile [k0, min(k0 + bn, n)) fixed (dK/dV kernel). Both must agree with the
+ * mask; bm is unused. */
 int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int bs, int bm, int need_full_rows);
 
 /* ---- tensor-core self test (GPU): C[128 x n] = A[128 x k] * B with the operand layouts the kernels use ---- */
