@@ -956,6 +956,15 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
+#ifdef FDA_PHASE_CLOCKS
+extern "C" int fda_debug_waits_bwd(unsigned long long* out256) {
+  static unsigned long long zero[256];
+  if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;
+  if (cudaMemcpyToSymbol(g_fda_wait, zero, sizeof(zero)) != cudaSuccess) return 1;
+  return 0;
+}
+#endif
+
 int read_status_bwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};
   FDA_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_fda_status, sizeof(int) * 4));

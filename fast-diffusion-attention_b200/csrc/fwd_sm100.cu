@@ -600,6 +600,15 @@ extern "C" int fda_debug_phase_clocks(unsigned long long* out8) {
 }
 #endif
 
+#ifdef FDA_PHASE_CLOCKS
+extern "C" int fda_debug_waits_fwd(unsigned long long* out256) {
+  static unsigned long long zero[256];
+  if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;
+  if (cudaMemcpyToSymbol(g_fda_wait, zero, sizeof(zero)) != cudaSuccess) return 1;
+  return 0;
+}
+#endif
+
 int read_status_fwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};
   FDA_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_fda_status, sizeof(int) * 4));
