@@ -54,6 +54,7 @@ struct BwdParams {
   int tiles_per_half;  // n_pad / 128
   int* ticket_kv;      // work counters of the two persistent kernels, zeroed before each launch
   int* ticket_q;
+  int wide_store;      // dq/dk/dv rows allow 32-byte stores
   float scale_log2, softcap_pre, softmax_scale;
 };
 
@@ -156,60 +157,50 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, u
 }
 
 // D[tmem, 128 x 128] = A[smem tile, rows x d] * B[smem tile, rows x d]^T, both K-major along d.
+// a_lo / b_lo are descriptor low words of the tiles (ptx::smem_desc_lo(addr, 16)).
 template <int kHeadDim>
-__device__ __forceinline__ void mma_rows_x_rows(uint32_t d_tmem, const uint8_t* a_tile, const uint8_t* b_tile,
-                                                uint32_t idesc) {
-  const uint32_t a0 = ptx::smem_u32(a_tile), b0 = ptx::smem_u32(b_tile);
+__device__ __forceinline__ void mma_rows_x_rows(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-    const uint32_t off = (kk / 4) * TileCfg<kHeadDim>::kPanelBytes + (kk % 4) * 32;
-    ptx::umma_ss_f16(d_tmem, ptx::make_smem_desc(a0 + off, 16, 1024), ptx::make_smem_desc(b0 + off, 16, 1024), idesc,
-                     kk > 0);
+    const uint32_t off = ((kk / 4) * TileCfg<kHeadDim>::kPanelBytes + (kk % 4) * 32) >> 4;
+    ptx::umma_ss_f16_lh(d_tmem, a_lo + off, b_lo + off, ptx::smem_desc_hi(1024), idesc, kk > 0);
   }
 }
+
+// Compute warpgroups of the two backward kernels: each owns kCols of the 128 columns of S / dP (all 128 lanes).
+constexpr int kCmpWG = 4;
+constexpr int kCols = kTile / kCmpWG;             // 32 columns per warpgroup
+constexpr int kCmpThreads = 128 * kCmpWG;         // 512
+constexpr int kBwdThreads = kCmpThreads + 64;     // + TMA warp + MMA warp
+constexpr int kLoadWarpB = 4 * kCmpWG;
+constexpr int kMmaWarpB = 4 * kCmpWG + 1;
+static_assert(kCols == 32, "one 32-column tensor-memory load per operand and warp");
 
 // D[tmem, 128 x d] (+)= A[tmem, 128 x 128 as 16-bit] * B[smem tile, 128 rows x d] (B MN-major: rows are the
-// reduction dimension). The A operand sits in two 32-column pieces: reduction rows 0-63 at a_tmem, 64-127 at
-// a_tmem + a_second_half.
+// reduction dimension). The A operand was written by the compute warpgroups in kCmpWG pieces of kCols
+// reduction rows (kCols/2 packed columns each); piece w starts at a_tmem + w * piece_stride.
 template <int kHeadDim>
-__device__ __forceinline__ void mma_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t a_second_half,
-                                                const uint8_t* b_tile, uint32_t idesc, bool accumulate) {
-  const uint32_t b0 = ptx::smem_u32(b_tile);
+__device__ __forceinline__ void mma_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t piece_stride,
+                                                uint32_t b_lo, uint32_t idesc, bool accumulate) {
+  // b_lo = ptx::smem_desc_lo(tile address, panel bytes): B is used MN-major, 16 reduction rows = 2048 bytes
 #pragma unroll
   for (int kk = 0; kk < kTile / 16; ++kk) {
-    const uint32_t a = a_tmem + (kk < 4 ? kk * 8 : a_second_half + (kk - 4) * 8);
-    ptx::umma_ts_f16(d_tmem, a, ptx::make_smem_desc(b0 + kk * 2048, TileCfg<kHeadDim>::kPanelBytes, 1024), idesc,
-                     (accumulate || kk > 0) ? 1u : 0u);
+    const uint32_t a = a_tmem + ((kk * 16) / kCols) * piece_stride + ((kk * 16) % kCols) / 2;
+    ptx::umma_ts_f16_lh(d_tmem, a, b_lo + kk * (2048 >> 4), ptx::smem_desc_hi(1024), idesc,
+                        (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
-// Store 32 fp32 accumulator columns of one row, scaled, as 16-bit, honouring head_dim.
-template <bool kBf16>
-__device__ __forceinline__ void store_row_chunk(uint16_t* row_ptr, int col0, const uint32_t* acc, float scale,
-                                                int head_dim) {
+// P and dS of kCols columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
+// lse2 / delta are per column (kPerColumn, read from shared memory) or per thread. kMasked is a template
+// parameter so that the common fully-visible tile carries no per-element compare/select at all.
+template <bool kBf16, bool kSoftcap, bool kPerColumn, bool kMasked, bool kNeedP>
+__device__ __forceinline__ void softmax_backward_cols(const uint32_t* s, const uint32_t* dp, const float* lse2_col,
+                                                      const float* delta_col, float lse2_row, float delta_row,
+                                                      float scale_log2, float softcap_pre, int lo, int hi,
+                                                      uint32_t* pk_p, uint32_t* pk_ds) {
 #pragma unroll
-  for (int i = 0; i < 32; i += 8) {
-    const int col = col0 + i;
-    if (col < head_dim) {
-      uint4 w;
-      w.x = ptx::pack2<kBf16>(__uint_as_float(acc[i + 0]) * scale, __uint_as_float(acc[i + 1]) * scale);
-      w.y = ptx::pack2<kBf16>(__uint_as_float(acc[i + 2]) * scale, __uint_as_float(acc[i + 3]) * scale);
-      w.z = ptx::pack2<kBf16>(__uint_as_float(acc[i + 4]) * scale, __uint_as_float(acc[i + 5]) * scale);
-      w.w = ptx::pack2<kBf16>(__uint_as_float(acc[i + 6]) * scale, __uint_as_float(acc[i + 7]) * scale);
-      *reinterpret_cast<uint4*>(row_ptr + col) = w;
-    }
-  }
-}
-
-// P and dS of 64 columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
-// lse2 / delta are per column (kPerColumn, read from shared memory) or per thread.
-template <bool kBf16, bool kSoftcap, bool kPerColumn>
-__device__ __forceinline__ void softmax_backward_64(const uint32_t* s, const uint32_t* dp, const float* lse2_col,
-                                                    const float* delta_col, float lse2_row, float delta_row,
-                                                    float scale_log2, float softcap_pre, bool masked, int lo,
-                                                    int hi, uint32_t* pk_p, uint32_t* pk_ds) {
-#pragma unroll
-  for (int c = 0; c < 64; c += 2) {
+  for (int c = 0; c < kCols; c += 2) {
     float pv[2], dsv[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -225,14 +216,14 @@ __device__ __forceinline__ void softmax_backward_64(const uint32_t* s, const uin
       float pr = ptx::ex2(fmaf(x, scale_log2, -l2));
       float d = pr * (__uint_as_float(dp[col]) - dl);
       if (kSoftcap) d *= dt;
-      if (masked && (col < lo || col >= hi)) {
+      if (kMasked && (col < lo || col >= hi)) {
         pr = 0.f;
         d = 0.f;
       }
       pv[e] = pr;
       dsv[e] = d;
     }
-    pk_p[c / 2] = ptx::pack2<kBf16>(pv[0], pv[1]);
+    if (kNeedP) pk_p[c / 2] = ptx::pack2<kBf16>(pv[0], pv[1]);
     pk_ds[c / 2] = ptx::pack2<kBf16>(dsv[0], dsv[1]);
   }
 }
@@ -292,13 +283,13 @@ struct DkdvCfg {
   using T = TileCfg<kHeadDim>;
   static constexpr int kStageBytes = 2 * T::kTileBytes + 1024;  // Q tile, dO tile, lse2[128], delta[128]
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
-  static constexpr int kThreads = 320;
+  static constexpr int kThreads = kBwdThreads;
   static constexpr int kTmemST = 0, kTmemDPT = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
   static_assert(256 + 2 * kHeadDim <= 512, "tensor memory budget");
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DkdvCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -321,7 +312,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 9);
+    sched_init(mbox, 4 * kCmpWG + 1);
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -329,11 +320,11 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
       ptx::mbar_init(&st_empty[i], 1);
     }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_full, 256);
+    ptx::mbar_init(pds_full, 4 * kCmpWG);
     ptx::mbar_init(acc_full, 1);
     ptx::fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == kLoadWarpB) {
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
   }
@@ -345,7 +336,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
   const int group = p.heads / p.heads_k;
   const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch;
 
-  if (warp == 8) {
+  if (warp == kLoadWarpB) {
     // ------------------------------------------------------------------------------------------------ producer
     if (lane == 0) {
       uint32_t n_item = 0, slot = 0;
@@ -386,12 +377,16 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
       }
       if (*abort_flag) __nanosleep(100000);
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarpB) {
     // ---------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      const uint32_t k_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
+      const uint32_t v_lo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
+      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);                  // K-major use
+      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), T::kPanelBytes);     // MN-major use
       uint32_t n_item = 0, slot = 0, cnt = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -412,16 +407,16 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
             const uint32_t stage = slot % kStages;
             if (!ptx::mbar_wait(&st_full[stage], (slot / kStages) & 1, abort_flag, 52)) { alive = false; break; }
             ptx::tc_fence_after();
-            const uint8_t* sQ = sStage + stage * Cfg::kStageBytes;
-            const uint8_t* sdO = sQ + T::kTileBytes;
-            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemST, sK, sQ, idesc_s);
-            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDPT, sV, sdO, idesc_s);
+            const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
+            const uint32_t do_off = q_off + (T::kTileBytes >> 4);
+            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemST, k_lo, st_lo_k + q_off, idesc_s);
+            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDPT, v_lo, st_lo_k + do_off, idesc_s);
             ptx::umma_commit(sdp_full);
             if (!ptx::mbar_wait(pds_full, cnt & 1, abort_flag, 53)) { alive = false; break; }
             ++cnt;
             ptx::tc_fence_after();
-            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDV, tmem + Cfg::kTmemST, 64, sdO, idesc_g, acc);
-            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDK, tmem + Cfg::kTmemDPT, 64, sQ, idesc_g, acc);
+            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDV, tmem + Cfg::kTmemST, kCols, st_lo_mn + do_off, idesc_g, acc);
+            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDK, tmem + Cfg::kTmemDPT, kCols, st_lo_mn + q_off, idesc_g, acc);
             acc = true;
             ptx::umma_commit(&st_empty[stage]);
             ++slot;
@@ -435,7 +430,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------------- softmax backward + epilogue
-    const int wg = warp >> 2;                  // which 64 query columns
+    const int wg = warp >> 2;                  // which kCols query columns
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // key row inside the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -462,34 +457,35 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
           if (cls == kTileSkip) continue;
           const uint32_t stage = slot % kStages;
           ++slot;
-          int lo = 0, hi = 0;
-          if (cls == kTileMasked) {
-            lo = (qh == it.kh ? same_lo : cross_lo) - (qa + wg * 64);
-            hi = (qh == it.kh ? same_hi : cross_hi) - (qa + wg * 64);
-          }
           const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * T::kTileBytes);
           // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
           if (!ptx::mbar_wait(&st_full[stage], ((slot - 1) / kStages) & 1, abort_flag, 60)) { alive = false; break; }
           if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 61)) { alive = false; break; }
           ++cnt;
           ptx::tc_fence_after();
-          uint32_t sv[64], dpv[64];
-          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * 64, sv);
-          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * 64 + 32, sv + 32);
-          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64, dpv);
-          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64 + 32, dpv + 32);
+          uint32_t sv[kCols], dpv[kCols];
+          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * kCols, sv);
+          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * kCols, dpv);
           ptx::tmem_wait_ld();
-          uint32_t pk_p[32], pk_ds[32];
-          softmax_backward_64<kBf16, kSoftcap, true>(sv, dpv, stats + wg * 64, stats + 128 + wg * 64, 0.f, 0.f,
-                                                     p.scale_log2, p.softcap_pre, cls == kTileMasked, lo, hi, pk_p,
-                                                     pk_ds);
-          // every warp of this warpgroup has its S^T / dP^T in registers only after its own loads; the two
-          // warpgroups write disjoint 32-column pieces inside their own 64 columns
-          ptx::tmem_st32(tmem + Cfg::kTmemST + lane_addr + wg * 64, pk_p);
-          ptx::tmem_st32(tmem + Cfg::kTmemDPT + lane_addr + wg * 64, pk_ds);
+          uint32_t pk_p[kCols / 2], pk_ds[kCols / 2];
+          if (cls == kTileMasked) {
+            const int lo = (qh == it.kh ? same_lo : cross_lo) - (qa + wg * kCols);
+            const int hi = (qh == it.kh ? same_hi : cross_hi) - (qa + wg * kCols);
+            softmax_backward_cols<kBf16, kSoftcap, true, true, true>(sv, dpv, stats + wg * kCols,
+                                                                      stats + 128 + wg * kCols, 0.f, 0.f, p.scale_log2,
+                                                                      p.softcap_pre, lo, hi, pk_p, pk_ds);
+          } else {
+            softmax_backward_cols<kBf16, kSoftcap, true, false, true>(sv, dpv, stats + wg * kCols,
+                                                                       stats + 128 + wg * kCols, 0.f, 0.f, p.scale_log2,
+                                                                       p.softcap_pre, 0, 0, pk_p, pk_ds);
+          }
+          // a warp overwrites only columns it has itself already loaded: its P^T / dS^T pieces (kCols/2 packed
+          // columns) go to the start of its own kCols columns of S^T / dP^T
+          ptx::tmem_st16(tmem + Cfg::kTmemST + lane_addr + wg * kCols, pk_p);
+          ptx::tmem_st16(tmem + Cfg::kTmemDPT + lane_addr + wg * kCols, pk_ds);
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
-          ptx::mbar_arrive(pds_full);
+          ptx::mbar_arrive_warp(pds_full);
         }
       }
       if (!alive) break;
@@ -499,24 +495,24 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
       {
         const bool key_valid = kj < it.n;
         const int64_t srow = static_cast<int64_t>(it.row0) + it.kh * it.n + kj;
-        uint16_t* dst;
-        uint32_t src;
-        float scale;
-        if (wg == 0) {
-          dst = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
-          src = tmem + Cfg::kTmemDK + lane_addr;
-          scale = p.softmax_scale;
-        } else {
-          dst = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
-          src = tmem + Cfg::kTmemDV + lane_addr;
-          scale = 1.f;
-        }
+        uint16_t* dk_row = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
+        uint16_t* dv_row = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
+        // dK and dV sit side by side in tensor memory: 2 * d / 32 chunks of 32 columns, dealt round-robin to the
+        // compute warpgroups
+        constexpr int kChunks = 2 * kHeadDim / 32;
 #pragma unroll
-        for (int c = 0; c < kHeadDim / 32; ++c) {
-          uint32_t acc[32];
-          ptx::tmem_ld32(src + c * 32, acc);
-          ptx::tmem_wait_ld();
-          if (key_valid) store_row_chunk<kBf16>(dst, c * 32, acc, scale, p.head_dim);
+        for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
+          const int gidx = g0 + wg;
+          if (gidx < kChunks) {
+            const bool is_dv = gidx * 32 >= kHeadDim;
+            const int col0 = gidx * 32 - (is_dv ? kHeadDim : 0);
+            uint32_t acc[32];
+            ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, acc);
+            ptx::tmem_wait_ld();
+            if (key_valid) {
+              ptx::store_row32<kBf16>(is_dv ? dv_row : dk_row, col0, acc, is_dv ? 1.f : p.softmax_scale, p.head_dim, p.wide_store != 0);
+            }
+          }
         }
       }
       ptx::tc_fence_before();
@@ -524,7 +520,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dkdv_kernel(const __grid_constant_
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+  if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -577,7 +573,7 @@ struct DqCfg {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DqCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -602,7 +598,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 9);
+    sched_init(mbox, 4 * kCmpWG + 1);
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -610,13 +606,13 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       ptx::mbar_init(&kv_empty[i], 1);
     }
     ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(sdp_free, 256);
-    ptx::mbar_init(ds_full, 256);
+    ptx::mbar_init(sdp_free, 4 * kCmpWG);
+    ptx::mbar_init(ds_full, 4 * kCmpWG);
     ptx::mbar_init(ds_free, 1);
     ptx::mbar_init(dq_full, 1);
     ptx::fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == kLoadWarpB) {
     ptx::tmem_alloc(tmem_slot, 512);
     ptx::tmem_relinquish();
   }
@@ -627,7 +623,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
   const int bs = p.block_size;
   const int total_items = p.tiles_per_half * 2 * p.heads * p.batch;
 
-  if (warp == 8) {
+  if (warp == kLoadWarpB) {
     if (lane == 0) {
       uint32_t n_item = 0, slot = 0;
       bool alive = true;
@@ -661,11 +657,15 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       }
       if (*abort_flag) __nanosleep(100000);
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarpB) {
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      const uint32_t q_lo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
+      const uint32_t do_lo = ptx::smem_desc_lo(ptx::smem_u32(sdO), 16);
+      const uint32_t kv_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sKV), 16);
+      const uint32_t kv_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV), T::kPanelBytes);
       uint32_t n_item = 0, slot = 0, cnt_sdp = 0, cnt_ds = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -689,8 +689,9 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
           if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 83)) return false;
           if (!ptx::mbar_wait(&kv_full[(slot_k + 1) % kStages], ((slot_k + 1) / kStages) & 1, abort_flag, 84)) return false;
           ptx::tc_fence_after();
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, sQ, sKV + (slot_k % kStages) * T::kTileBytes, idesc_s);
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, sdO, sKV + ((slot_k + 1) % kStages) * T::kTileBytes, idesc_s);
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, q_lo, kv_lo_k + (slot_k % kStages) * (T::kTileBytes >> 4), idesc_s);
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, do_lo, kv_lo_k + ((slot_k + 1) % kStages) * (T::kTileBytes >> 4),
+                                    idesc_s);
           ptx::umma_commit(sdp_full);
           ptx::umma_commit(&kv_empty[(slot_k + 1) % kStages]);  // V tile no longer needed
           return true;
@@ -704,8 +705,8 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
           if (!ptx::mbar_wait(ds_full, cnt_ds & 1, abort_flag, 85)) { alive = false; break; }
           ++cnt_ds;
           ptx::tc_fence_after();
-          mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS, 32, sKV + (slot_k % kStages) * T::kTileBytes,
-                                    idesc_g, j > 0);
+          mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS, kCols / 2,
+                                    kv_lo_mn + (slot_k % kStages) * (T::kTileBytes >> 4), idesc_g, j > 0);
           ptx::umma_commit(&kv_empty[slot_k % kStages]);
           ptx::umma_commit(ds_free);
         }
@@ -717,7 +718,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       }
     }
   } else {
-    const int wg = warp >> 2;                  // which 64 key columns
+    const int wg = warp >> 2;                  // which kCols key columns
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // query row inside the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
@@ -748,29 +749,32 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
           if (it.qh == 1) { lo = 0; hi = blk1; }
           else if (kh == 1) { lo = 0; hi = blk0; }
           else { lo = blk0; hi = blk1; }
-          lo -= kt * kTile + wg * 64;
-          hi -= kt * kTile + wg * 64;
+          lo -= kt * kTile + wg * kCols;
+          hi -= kt * kTile + wg * kCols;
         }
         if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 91)) { alive = false; break; }
         ptx::tc_fence_after();
-        uint32_t sv[64], dpv[64];
-        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * 64, sv);
-        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * 64 + 32, sv + 32);
-        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * 64, dpv);
-        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * 64 + 32, dpv + 32);
+        uint32_t sv[kCols], dpv[kCols];
+        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * kCols, sv);
+        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * kCols, dpv);
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(sdp_free);
-        uint32_t pk_p[32], pk_ds[32];
-        softmax_backward_64<kBf16, kSoftcap, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
-                                                    p.softcap_pre, cls == kTileMasked, lo, hi, pk_p, pk_ds);
+        ptx::mbar_arrive_warp(sdp_free);
+        uint32_t pk_ds[kCols / 2];
+        if (cls == kTileMasked) {
+          softmax_backward_cols<kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
+                                                                      p.softcap_pre, lo, hi, nullptr, pk_ds);
+        } else {
+          softmax_backward_cols<kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
+                                                                       p.softcap_pre, 0, 0, nullptr, pk_ds);
+        }
         if (!ptx::mbar_wait(ds_free, (cnt & 1) ^ 1, abort_flag, 92)) { alive = false; break; }
         ++cnt;
         ptx::tc_fence_after();
-        ptx::tmem_st32(tmem + Cfg::kTmemDS + lane_addr + wg * 32, pk_ds);
+        ptx::tmem_st16(tmem + Cfg::kTmemDS + lane_addr + wg * (kCols / 2), pk_ds);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(ds_full);
+        ptx::mbar_arrive_warp(ds_full);
       }
       if (!alive) break;
       if (!ptx::mbar_wait(dq_full, n_item & 1, abort_flag, 93)) break;
@@ -779,14 +783,16 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
       {
         const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
         uint16_t* dst = static_cast<uint16_t*>(p.dq) + it.bcoord * p.dq_bs + srow * p.dq_rs + it.h * p.dq_hs;
-        constexpr int kChunks = kHeadDim / 64;  // 32-column chunks per warpgroup
+        constexpr int kChunks = kHeadDim / 32;  // 32-column chunks, dealt round-robin to the warpgroups
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-          const int col0 = (wg * kChunks + c) * 32;
-          uint32_t acc[32];
-          ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + col0, acc);
-          ptx::tmem_wait_ld();
-          if (row_valid) store_row_chunk<kBf16>(dst, col0, acc, p.softmax_scale, p.head_dim);
+        for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
+          const int gidx = g0 + wg;
+          if (gidx < kChunks) {
+            uint32_t acc[32];
+            ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + gidx * 32, acc);
+            ptx::tmem_wait_ld();
+            if (row_valid) ptx::store_row32<kBf16>(dst, gidx * 32, acc, p.softmax_scale, p.head_dim, p.wide_store != 0);
+          }
         }
       }
       ptx::tc_fence_before();
@@ -794,7 +800,7 @@ __global__ void __launch_bounds__(320, 1) bwd_dq_kernel(const __grid_constant__ 
   }
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+  if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
 template <typename Kernel>
@@ -829,7 +835,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     if (rc) return rc;
     const int items = p.tiles_per_half * 2 * p.heads * p.batch;
     const int grid = items < sm_count ? items : sm_count;
-    kernel<<<grid, 320, Cfg::kSmemBytes, stream>>>(p);
+    kernel<<<grid, kBwdThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
   return FDA_OK;
@@ -890,6 +896,14 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
     if ((reinterpret_cast<uintptr_t>(t->ptr) & 15) || (t->row_stride % 8) || (t->head_stride % 8) ||
         (!varlen && (t->batch_stride % 8))) {
       return FDA_ERR_STRIDE;
+    }
+  }
+  p.wide_store = (d % 16 == 0) ? 1 : 0;
+  const FdaTensor* grads[] = {&a.dq, &a.dk, &a.dv};
+  for (const FdaTensor* t : grads) {
+    if ((reinterpret_cast<uintptr_t>(t->ptr) & 31) || (t->row_stride % 16) || (t->head_stride % 16) ||
+        (!varlen && (t->batch_stride % 16))) {
+      p.wide_store = 0;
     }
   }
   p.out = a.out.ptr;
@@ -956,7 +970,7 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
-#ifdef FDA_PHASE_CLOCKS
+#ifdef FDA_WAIT_CLOCKS
 extern "C" int fda_debug_waits_bwd(unsigned long long* out256) {
   static unsigned long long zero[256];
   if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;

@@ -32,7 +32,7 @@ namespace {
 #ifdef FDA_PHASE_CLOCKS
 // Debug build only: cycles one softmax thread spends per phase, summed over CTAs (wait, load, math, store,
 // epilogue/other) and the number of tile steps.
-__device__ unsigned long long g_fda_phase[8];
+__device__ unsigned long long g_fda_phase[16];
 #endif
 
 constexpr int kBlockM = 128;  // query rows per tile (= tensor-memory lanes)
@@ -40,6 +40,10 @@ constexpr int kBlockN = 128;  // keys per tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+#ifndef FDA_MUFU_LOCK
+#define FDA_MUFU_LOCK 0
+#endif
+constexpr bool kUseMufuLock = FDA_MUFU_LOCK != 0;  // turn-taking of the two softmax warpgroups (experiment)
 
 struct FwdParams {
   CUtensorMap tm_q, tm_k, tm_v;
@@ -51,6 +55,7 @@ struct FwdParams {
   int items_per_half;  // ceil(max n / rows per item)
   int total_items;
   int* ticket;         // global work counter, zeroed before the launch
+  int wide_store;      // rows of out allow 32-byte stores
   float scale_log2;    // exponent scale: softmax_scale*log2(e), or softcap*log2(e) with softcapping
   float softcap_pre;   // softmax_scale / softcap (tanh argument scale)
   float lse_scale;     // natural-log scale of the row maximum: softmax_scale, or softcap
@@ -148,6 +153,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kQTiles);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
+  int* mufu_lock = reinterpret_cast<int*>(mbox + 1);  // one per warp quadrant (= SM sub-partition)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -155,6 +161,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kQTiles + 1);
+    for (int i = 0; i < 4; ++i) mufu_lock[i] = 0;
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -163,7 +170,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
     }
     for (int t = 0; t < kQTiles; ++t) {
       ptx::mbar_init(&s_full[t], 1);
-      ptx::mbar_init(&p_full[t], 128);
+      ptx::mbar_init(&p_full[t], 4);  // one arrival per softmax warp
       ptx::mbar_init(&o_full[t], 1);
     }
     ptx::fence_mbar_init();
@@ -242,23 +249,26 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       for (int t = 0; t < kQTiles; ++t) cnt_p[t] = 0;
       bool alive = true;
 
+      // descriptor low words of stage 0 / tile 0; a stage or tile step adds kTileBytes / 16, a k-step a constant
+      constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);
+      const uint32_t q_lo0 = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
+      const uint32_t k_lo0 = ptx::smem_desc_lo(ptx::smem_u32(sKV), 16);
+      const uint32_t v_lo0 = ptx::smem_desc_lo(ptx::smem_u32(sKV), Cfg::kPanelBytes);
       auto issue_s = [&](int t, uint32_t k_stage) {
-        const uint32_t a0 = ptx::smem_u32(sQ + t * Cfg::kTileBytes);
-        const uint32_t b0 = ptx::smem_u32(sKV + k_stage * Cfg::kTileBytes);
+        const uint32_t a_lo = q_lo0 + t * (Cfg::kTileBytes >> 4);
+        const uint32_t b_lo = k_lo0 + k_stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-          const uint32_t off = (kk / 4) * Cfg::kPanelBytes + (kk % 4) * 32;
-          ptx::umma_ss_f16(tmem + Cfg::kTmemS + t * 128, ptx::make_smem_desc(a0 + off, 16, 1024),
-                           ptx::make_smem_desc(b0 + off, 16, 1024), idesc_s, kk > 0);
+          const uint32_t off = ((kk / 4) * Cfg::kPanelBytes + (kk % 4) * 32) >> 4;
+          ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS + t * 128, a_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
         }
       };
       auto issue_pv = [&](int t, uint32_t v_stage, bool accumulate) {
-        const uint32_t b0 = ptx::smem_u32(sKV + v_stage * Cfg::kTileBytes);
+        const uint32_t b_lo = v_lo0 + v_stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          ptx::umma_ts_f16(tmem + Cfg::kTmemO + t * kHeadDim, tmem + Cfg::kTmemS + t * 128 + kk * 8,
-                           ptx::make_smem_desc(b0 + kk * 2048, Cfg::kPanelBytes, 1024), idesc_o,
-                           (accumulate || kk > 0) ? 1u : 0u);
+          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemO + t * kHeadDim, tmem + Cfg::kTmemS + t * 128 + kk * 8,
+                              b_lo + kk * (2048 >> 4), kDescHi, idesc_o, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
 
@@ -329,14 +339,16 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
     uint32_t cnt_s = 0, cnt_o = 0;
     bool alive = true;
 #ifdef FDA_PHASE_CLOCKS
-    long long ph_wait = 0, ph_ld = 0, ph_math = 0, ph_st = 0, ph_epi = 0, ph_steps = 0, ph_t = 0, ph_owait = 0, ph_pre = 0;
+    long long ph_wait = 0, ph_ld = 0, ph_math = 0, ph_st = 0, ph_epi = 0, ph_steps = 0, ph_t = 0, ph_owait = 0, ph_pre = 0, ph_sched = 0, ph_setup = 0;
 #define FDA_PH(acc) do { const long long _n = clock64(); acc += _n - ph_t; ph_t = _n; } while (0)
     ph_t = clock64();
 #else
 #define FDA_PH(acc) do {} while (0)
 #endif
     for (uint32_t n_sched = 0; alive; ++n_sched) {
+      FDA_PH(ph_pre);
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      FDA_PH(ph_sched);
       if (idx < 0 || idx >= p.total_items) break;
       const Item it = decode_item<kQTiles>(p, idx);
       if (!it.valid) continue;
@@ -353,6 +365,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       float m_run = -INFINITY;  // reference maximum (unscaled scores, or tanh values with softcap)
       float l_run = 0.f;
       bool o_started = false;
+      FDA_PH(ph_setup);
       for (int s = 0; s < steps && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
@@ -371,6 +384,18 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
           ptx::tmem_wait_ld();
         }
         FDA_PH(ph_ld);
+        // The two warps that share an SM sub-partition (same quadrant, one per query tile) take turns in the
+        // exp-heavy part: whoever gets its S first runs at full MUFU rate and hands its P to the MMA warp early,
+        // so the tensor pipe works on one tile while the other tile is in its softmax. Only a scheduling hint:
+        // nothing is protected by the lock, and a warp that cannot get it in time goes ahead without it.
+        bool have_lock = false;
+        if (kQTiles > 1 && kUseMufuLock) {
+          if (lane == 0) {
+            int spins = 0;
+            while (!(have_lock = (atomicCAS(&mufu_lock[quad], 0, 1) == 0)) && ++spins < 20000) {}
+          }
+          have_lock = __shfl_sync(0xffffffffu, have_lock ? 1 : 0, 0) != 0;
+        }
         if (kSoftcap) {
 #pragma unroll
           for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * p.softcap_pre);
@@ -387,9 +412,18 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
             if (c < lo || c >= hi) v[c] = -INFINITY;
           }
         }
-        float m_tile = v[0];
+        // eight independent running maxima (a single chain of 127 dependent max operations costs more than the
+        // exponentials that follow)
+        float mx[8];
 #pragma unroll
-        for (int c = 1; c < kBlockN; ++c) m_tile = fmaxf(m_tile, v[c]);
+        for (int i = 0; i < 8; ++i) mx[i] = v[i];
+#pragma unroll
+        for (int c = 8; c < kBlockN; c += 8) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], v[c + i]);
+        }
+        const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                   fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         const float m_new = fmaxf(m_run, m_tile);
         // advance the reference maximum only when it grew by more than the threshold (always on the first tile)
         const bool need = (m_new - m_run) * p.scale_log2 > kRescaleThreshold;
@@ -411,22 +445,26 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         }
         const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
         const float neg_m = -m_ref * p.scale_log2;
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[kBlockN / 2];
 #pragma unroll
         for (int c = 0; c < kBlockN; c += 2) {
           const float p0 = ptx::ex2(fmaf(v[c], p.scale_log2, neg_m));
           const float p1 = ptx::ex2(fmaf(v[c + 1], p.scale_log2, neg_m));
-          sum += p0 + p1;
+          sum4[(c / 2) & 3] += p0 + p1;
           pk[c / 2] = ptx::pack2<kBf16>(p0, p1);
         }
-        l_run += sum;
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (kQTiles > 1 && kUseMufuLock) {
+          __syncwarp();
+          if (lane == 0 && have_lock) atomicExch(&mufu_lock[quad], 0);
+        }
         FDA_PH(ph_math);
 #pragma unroll
         for (int c = 0; c < kBlockN / 64; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(&p_full[t]);
+        ptx::mbar_arrive_warp(&p_full[t]);
         o_started = true;
         FDA_PH(ph_st);
 #ifdef FDA_PHASE_CLOCKS
@@ -442,26 +480,22 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       ptx::tc_fence_after();
       const float inv_l = 1.f / l_run;
       const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
-      if (kBf16 || !kBf16) {
+      {
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + it.bcoord * p.o_batch_stride + srow * p.o_row_stride +
                          it.h * p.o_head_stride;
+        // all loads first, one wait: the stores of a chunk then overlap the conversion of the next
+        uint32_t o[kHeadDim <= 128 ? kHeadDim : 128];
+        constexpr int kPass = kHeadDim <= 128 ? 1 : kHeadDim / 128;
 #pragma unroll
-        for (int c = 0; c < kHeadDim / 32; ++c) {
-          uint32_t o[32];
-          ptx::tmem_ld32(tmem_o + c * 32, o);
+        for (int pass = 0; pass < kPass; ++pass) {
+          constexpr int kPassCols = kHeadDim <= 128 ? kHeadDim : 128;
+#pragma unroll
+          for (int c = 0; c < kPassCols / 32; ++c) ptx::tmem_ld32(tmem_o + pass * 128 + c * 32, o + c * 32);
           ptx::tmem_wait_ld();
           if (row_valid) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              const int col = c * 32 + i;
-              if (col < p.head_dim) {  // head_dim is a multiple of 8
-                uint4 w;
-                w.x = ptx::pack2<kBf16>(__uint_as_float(o[i + 0]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                w.y = ptx::pack2<kBf16>(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                w.z = ptx::pack2<kBf16>(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                w.w = ptx::pack2<kBf16>(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                *reinterpret_cast<uint4*>(orow + col) = w;
-              }
+            for (int c = 0; c < kPassCols / 32; ++c) {
+              ptx::store_row32<kBf16>(orow, pass * 128 + c * 32, o + c * 32, inv_l, p.head_dim, p.wide_store != 0);
             }
           }
         }
@@ -479,6 +513,8 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
     }
 #ifdef FDA_PHASE_CLOCKS
     if (threadIdx.x == 0) {
+      atomicAdd(&g_fda_phase[8], (unsigned long long)ph_sched);
+      atomicAdd(&g_fda_phase[9], (unsigned long long)ph_setup);
       atomicAdd(&g_fda_phase[6], (unsigned long long)ph_owait);
       atomicAdd(&g_fda_phase[7], (unsigned long long)ph_pre);
       atomicAdd(&g_fda_phase[0], (unsigned long long)ph_wait);
@@ -557,6 +593,10 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   p.o_batch_stride = varlen ? 0 : a.out.batch_stride;
   p.o_row_stride = a.out.row_stride;
   p.o_head_stride = a.out.head_stride;
+  p.wide_store = (d % 16 == 0 && (reinterpret_cast<uintptr_t>(a.out.ptr) & 31) == 0 && a.out.row_stride % 16 == 0 &&
+                  a.out.head_stride % 16 == 0 && (varlen || a.out.batch_stride % 16 == 0))
+                     ? 1
+                     : 0;
   p.cu_seqlens = pr.cu_seqlens;
   p.batch = pr.batch;
   p.seqlen = pr.seqlen;
@@ -593,14 +633,14 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
 
 #ifdef FDA_PHASE_CLOCKS
 extern "C" int fda_debug_phase_clocks(unsigned long long* out8) {
-  unsigned long long zero[8] = {0};
+  unsigned long long zero[16] = {0};
   if (cudaMemcpyFromSymbol(out8, g_fda_phase, sizeof(zero)) != cudaSuccess) return 1;
   if (cudaMemcpyToSymbol(g_fda_phase, zero, sizeof(zero)) != cudaSuccess) return 1;
   return 0;
 }
 #endif
 
-#ifdef FDA_PHASE_CLOCKS
+#ifdef FDA_WAIT_CLOCKS
 extern "C" int fda_debug_waits_fwd(unsigned long long* out256) {
   static unsigned long long zero[256];
   if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;

@@ -47,6 +47,12 @@ __device__ __forceinline__ void fence_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for the whole warp, made by lane 0 after every lane has reached this point (each lane has done its
+// own tcgen05 wait + fence before calling). 128 separate arrivals on one barrier serialise; 4 do not.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -89,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, v
   return true;
 }
 
-#ifdef FDA_PHASE_CLOCKS
+#ifdef FDA_WAIT_CLOCKS
 }  // namespace ptx
 // Debug build only: cycles spent inside each wait site (indexed by its code) and the number of waits, recorded by
 // lane 0 of the first compute warp and of the producer / MMA warps.
@@ -227,6 +233,37 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
+// The same descriptor split in two 32-bit words so that the MMA-issuing thread does one integer add per MMA:
+// the high word (stride offset, version, swizzle mode) is a compile-time constant, the low word is
+// (address / 16) | (leading offset / 16) << 16 and advances by (byte offset / 16).
+__host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t stride_bytes) {
+  return ((stride_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr, uint32_t leading_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((leading_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ void umma_ss_f16_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_f16_lh(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---- tensor-memory loads / stores: 32 lanes x 32-bit, N consecutive columns per thread -------------------------
 // Warp w of a warpgroup may only touch lanes 32*(w%4) .. +31; lane field = bits 31-16 of the address.
 #define FDA_R4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
@@ -274,6 +311,13 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 #undef FDA_R4
 #undef FDA_W4
 
+// 256-bit global store (one full 32-byte sector per thread); the address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 // ---- small math helpers --------------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -298,6 +342,31 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return kBf16 ? pack_bf16(lo, hi) : pack_f16(lo, hi);
+}
+
+// Store 32 fp32 accumulator values of one row as 16-bit after scaling: columns [col0, col0 + 32) of a row of
+// `head_dim` (a multiple of 8) elements. `wide` = the row pointer and head_dim allow 32-byte stores.
+template <bool kBf16>
+__device__ __forceinline__ void store_row32(uint16_t* row_ptr, int col0, const uint32_t* acc, float scale,
+                                            int head_dim, bool wide) {
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    w[i] = pack2<kBf16>(__uint_as_float(acc[2 * i]) * scale, __uint_as_float(acc[2 * i + 1]) * scale);
+  }
+  if (wide) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 16) {
+      if (col0 + i < head_dim) st_global_v8(row_ptr + col0 + i, w + i / 2);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      if (col0 + i < head_dim) {
+        *reinterpret_cast<uint4*>(row_ptr + col0 + i) = make_uint4(w[i / 2], w[i / 2 + 1], w[i / 2 + 2], w[i / 2 + 3]);
+      }
+    }
+  }
 }
 
 }  // namespace ptx
