@@ -35,6 +35,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;
+  CUtensorMap tm_q64, tm_do64;  // same tensors, 64-row boxes (dK/dV kernel)
   const void* out;
   const void* dout;
   void* dq;
@@ -191,16 +192,16 @@ __device__ __forceinline__ void mma_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem
   }
 }
 
-// P and dS of kCols columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
+// P and dS of kN columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
 // lse2 / delta are per column (kPerColumn, read from shared memory) or per thread. kMasked is a template
 // parameter so that the common fully-visible tile carries no per-element compare/select at all.
-template <bool kBf16, bool kSoftcap, bool kPerColumn, bool kMasked, bool kNeedP>
+template <int kN, bool kBf16, bool kSoftcap, bool kPerColumn, bool kMasked, bool kNeedP>
 __device__ __forceinline__ void softmax_backward_cols(const uint32_t* s, const uint32_t* dp, const float* lse2_col,
                                                       const float* delta_col, float lse2_row, float delta_row,
                                                       float scale_log2, float softcap_pre, int lo, int hi,
                                                       uint32_t* pk_p, uint32_t* pk_ds) {
 #pragma unroll
-  for (int c = 0; c < kCols; c += 2) {
+  for (int c = 0; c < kN; c += 2) {
     float pv[2], dsv[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -278,14 +279,30 @@ __device__ __forceinline__ KvSpans make_kv_spans(const KvItem& it, int bs) {
   return sp;
 }
 
+// The query side streams in sub-tiles of kSub = 64 rows so that S^T / dP^T (64 columns each) can be double
+// buffered in tensor memory next to the dK / dV accumulators: while the compute warps turn buffer u into
+// P^T / dS^T, the tensor pipe runs dV / dK of the previous sub-tile and S^T / dP^T of the next one.
+constexpr int kSub = 64;
+constexpr int kSubCols = kSub / kCmpWG;  // 16 query columns per compute warpgroup
+
 template <int kHeadDim, int kStages>
 struct DkdvCfg {
   using T = TileCfg<kHeadDim>;
-  static constexpr int kStageBytes = 2 * T::kTileBytes + 1024;  // Q tile, dO tile, lse2[128], delta[128]
+  static constexpr int kSubTileBytes = kSub * kHeadDim * 2;     // Q or dO sub-tile
+  static constexpr int kSubPanelBytes = kSub * 128;             // one 64-column panel of a sub-tile
+  static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64]
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
   static constexpr int kThreads = kBwdThreads;
-  static constexpr int kTmemST = 0, kTmemDPT = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
+  // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
+  static constexpr int kTmemDK = 256, kTmemDV = 256 + kHeadDim;
   static_assert(256 + 2 * kHeadDim <= 512, "tensor memory budget");
+  static_assert(kStageBytes % 1024 == 0, "sub-tiles must stay 1024-byte aligned for the 128-byte swizzle");
+};
+
+// Sub-steps of one item: query heads of the group x visible 128-row query tiles x two 64-row halves; a half
+// with no visible row is skipped. All roles walk this sequence identically.
+struct SubStep {
+  int h, qh, sa, sb, cls;
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
@@ -302,9 +319,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   uint64_t* kv_empty = bars + 1;
   uint64_t* st_full = bars + 2;
   uint64_t* st_empty = st_full + kStages;
-  uint64_t* sdp_full = st_empty + kStages;
-  uint64_t* pds_full = sdp_full + 1;
-  uint64_t* acc_full = pds_full + 1;
+  uint64_t* sdp_full = st_empty + kStages;   // [2]
+  uint64_t* pds_full = sdp_full + 2;         // [2]
+  uint64_t* acc_full = pds_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
@@ -319,8 +336,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       ptx::mbar_init(&st_full[i], 1);
       ptx::mbar_init(&st_empty[i], 1);
     }
-    ptx::mbar_init(sdp_full, 1);
-    ptx::mbar_init(pds_full, 4 * kCmpWG);
+    for (int u = 0; u < 2; ++u) {
+      ptx::mbar_init(&sdp_full[u], 1);
+      ptx::mbar_init(&pds_full[u], 4 * kCmpWG);
+    }
     ptx::mbar_init(acc_full, 1);
     ptx::fence_mbar_init();
   }
@@ -336,10 +355,35 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   const int group = p.heads / p.heads_k;
   const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch;
 
+  // Calls fn(SubStep) for every non-skipped sub-step of the item, in order; stops early when fn returns false.
+  auto for_each_substep = [&](const KvItem& it, const QueryPlan& plan, const KvSpans& spans, auto&& fn) -> bool {
+    for (int g = 0; g < group; ++g) {
+      for (int s = 0; s < plan.steps(); ++s) {
+        int qh, qt;
+        plan.step(s, it.kh, qh, qt);
+        const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
+        if (spans.classify(qh, it.kh, qa, qb) == kTileSkip) continue;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          SubStep st;
+          st.sa = qa + half * kSub;
+          if (st.sa >= qb) continue;
+          st.sb = imin(st.sa + kSub, qb);
+          st.cls = spans.classify(qh, it.kh, st.sa, st.sb);
+          if (st.cls == kTileSkip) continue;
+          st.h = it.hk * group + g;
+          st.qh = qh;
+          if (!fn(st)) return false;
+        }
+      }
+    }
+    return true;
+  };
+
   if (warp == kLoadWarpB) {
     // ------------------------------------------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t n_item = 0, slot = 0;
+      uint32_t n_item = 0, gc = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_produce(mbox, n_sched, p.ticket_kv, abort_flag);
@@ -353,26 +397,24 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         const int k_row = it.row0 + it.kh * it.n + it.k0;
         load_tile<kHeadDim>(sK, &p.tm_k, kv_full, k_row, it.hk, it.bcoord);
         load_tile<kHeadDim>(sV, &p.tm_v, kv_full, k_row, it.hk, it.bcoord);
-        for (int g = 0; g < group && alive; ++g) {
-          const int h = it.hk * group + g;
-          for (int s = 0; s < plan.steps(); ++s) {
-            int qh, qt;
-            plan.step(s, it.kh, qh, qt);
-            const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-            if (spans.classify(qh, it.kh, qa, qb) == kTileSkip) continue;
-            const uint32_t stage = slot % kStages;
-            if (!ptx::mbar_wait(&st_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 42)) { alive = false; break; }
-            uint8_t* base = sStage + stage * Cfg::kStageBytes;
-            ptx::mbar_expect_tx(&st_full[stage], 2 * T::kTileBytes + 1024);
-            const int q_row = it.row0 + qh * it.n + qa;
-            load_tile<kHeadDim>(base, &p.tm_q, &st_full[stage], q_row, h, it.bcoord);
-            load_tile<kHeadDim>(base + T::kTileBytes, &p.tm_do, &st_full[stage], q_row, h, it.bcoord);
-            const int64_t seg = stat_segment(p, it.b, h, qh) + qa;
-            ptx::bulk_load_1d(base + 2 * T::kTileBytes, p.lse2_pad + seg, 512, &st_full[stage]);
-            ptx::bulk_load_1d(base + 2 * T::kTileBytes + 512, p.delta_pad + seg, 512, &st_full[stage]);
-            ++slot;
+        alive = for_each_substep(it, plan, spans, [&](const SubStep& st) -> bool {
+          const uint32_t stage = gc % kStages;
+          if (!ptx::mbar_wait(&st_empty[stage], ((gc / kStages) & 1) ^ 1, abort_flag, 42)) return false;
+          uint8_t* base = sStage + stage * Cfg::kStageBytes;
+          ptx::mbar_expect_tx(&st_full[stage], 2 * Cfg::kSubTileBytes + 512);
+          const int q_row = it.row0 + st.qh * it.n + st.sa;
+#pragma unroll
+          for (int c = 0; c < T::kPanels; ++c) {
+            ptx::tma_load_4d(base + c * Cfg::kSubPanelBytes, &p.tm_q64, &st_full[stage], c * 64, q_row, st.h, it.bcoord);
+            ptx::tma_load_4d(base + Cfg::kSubTileBytes + c * Cfg::kSubPanelBytes, &p.tm_do64, &st_full[stage], c * 64,
+                             q_row, st.h, it.bcoord);
           }
-        }
+          const int64_t seg = stat_segment(p, it.b, st.h, st.qh) + st.sa;
+          ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes, p.lse2_pad + seg, 256, &st_full[stage]);
+          ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes + 256, p.delta_pad + seg, 256, &st_full[stage]);
+          ++gc;
+          return true;
+        });
         ++n_item;
       }
       if (*abort_flag) __nanosleep(100000);
@@ -381,14 +423,41 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     // ---------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
-      const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
+      const uint32_t idesc_s = ptx::make_idesc(kTile, kSub, kFmt, false, false);
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
       const uint32_t k_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t v_lo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
-      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);                  // K-major use
-      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), T::kPanelBytes);     // MN-major use
-      uint32_t n_item = 0, slot = 0, cnt = 0;
+      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);                      // K-major use
+      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), Cfg::kSubPanelBytes);    // MN-major use
+      uint32_t n_item = 0, g_issued = 0, g_done = 0;
       bool alive = true;
+      bool acc = false;
+
+      // dV += P^T dO and dK += dS^T Q of the oldest sub-step whose S^T / dP^T are outstanding
+      auto retire = [&]() -> bool {
+        const uint32_t u = g_done & 1u, stage = g_done % kStages;
+        if (!ptx::mbar_wait(&pds_full[u], (g_done >> 1) & 1u, abort_flag, 53)) return false;
+        ptx::tc_fence_after();
+        const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
+        const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
+        const uint32_t st_t = tmem + u * 128, dpt_t = tmem + u * 128 + 64;
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk) {
+          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols, st_lo_mn + do_off + kk * (2048 >> 4), kHi, idesc_g,
+                              (acc || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < kSub / 16; ++kk) {
+          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDK, dpt_t + kk * kSubCols, st_lo_mn + q_off + kk * (2048 >> 4), kHi, idesc_g,
+                              (acc || kk > 0) ? 1u : 0u);
+        }
+        acc = true;
+        ptx::umma_commit(&st_empty[stage]);
+        ++g_done;
+        return true;
+      };
+
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
         if (idx < 0 || idx >= total_items) break;
@@ -397,31 +466,33 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
         const KvSpans spans = make_kv_spans(it, bs);
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
-        bool acc = false;
-        for (int g = 0; g < group && alive; ++g) {
-          for (int s = 0; s < plan.steps(); ++s) {
-            int qh, qt;
-            plan.step(s, it.kh, qh, qt);
-            const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-            if (spans.classify(qh, it.kh, qa, qb) == kTileSkip) continue;
-            const uint32_t stage = slot % kStages;
-            if (!ptx::mbar_wait(&st_full[stage], (slot / kStages) & 1, abort_flag, 52)) { alive = false; break; }
-            ptx::tc_fence_after();
-            const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
-            const uint32_t do_off = q_off + (T::kTileBytes >> 4);
-            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemST, k_lo, st_lo_k + q_off, idesc_s);
-            mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDPT, v_lo, st_lo_k + do_off, idesc_s);
-            ptx::umma_commit(sdp_full);
-            if (!ptx::mbar_wait(pds_full, cnt & 1, abort_flag, 53)) { alive = false; break; }
-            ++cnt;
-            ptx::tc_fence_after();
-            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDV, tmem + Cfg::kTmemST, kCols, st_lo_mn + do_off, idesc_g, acc);
-            mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDK, tmem + Cfg::kTmemDPT, kCols, st_lo_mn + q_off, idesc_g, acc);
-            acc = true;
-            ptx::umma_commit(&st_empty[stage]);
-            ++slot;
+        acc = false;
+        alive = for_each_substep(it, plan, spans, [&](const SubStep&) -> bool {
+          if (g_issued - g_done == 2) {
+            if (!retire()) return false;
           }
-        }
+          const uint32_t u = g_issued & 1u, stage = g_issued % kStages;
+          if (!ptx::mbar_wait(&st_full[stage], (g_issued / kStages) & 1u, abort_flag, 52)) return false;
+          ptx::tc_fence_after();
+          const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
+          const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            const uint32_t b_off = ((kk / 4) * Cfg::kSubPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + u * 128, k_lo + a_off, st_lo_k + q_off + b_off, kHi, idesc_s, kk > 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            const uint32_t b_off = ((kk / 4) * Cfg::kSubPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + u * 128 + 64, v_lo + a_off, st_lo_k + do_off + b_off, kHi, idesc_s, kk > 0);
+          }
+          ptx::umma_commit(&sdp_full[u]);
+          ++g_issued;
+          return true;
+        });
+        while (alive && g_done < g_issued) alive = retire();
         if (!alive) break;
         ptx::umma_commit(kv_empty);
         ptx::umma_commit(acc_full);
@@ -430,11 +501,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     }
   } else {
     // ------------------------------------------------------------------------- softmax backward + epilogue
-    const int wg = warp >> 2;                  // which kCols query columns
+    const int wg = warp >> 2;                  // which kSubCols query columns of a sub-tile
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // key row inside the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint32_t n_item = 0, slot = 0, cnt = 0;
+    uint32_t n_item = 0, gc = 0;
     bool alive = true;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
@@ -448,46 +519,41 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       int same_lo, same_hi, cross_lo, cross_hi;
       query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
       query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
-      for (int g = 0; g < group && alive; ++g) {
-        for (int s = 0; s < plan.steps(); ++s) {
-          int qh, qt;
-          plan.step(s, it.kh, qh, qt);
-          const int qa = qt * kTile, qb = imin(qa + kTile, it.n);
-          const int cls = spans.classify(qh, it.kh, qa, qb);
-          if (cls == kTileSkip) continue;
-          const uint32_t stage = slot % kStages;
-          ++slot;
-          const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * T::kTileBytes);
-          // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
-          if (!ptx::mbar_wait(&st_full[stage], ((slot - 1) / kStages) & 1, abort_flag, 60)) { alive = false; break; }
-          if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 61)) { alive = false; break; }
-          ++cnt;
-          ptx::tc_fence_after();
-          uint32_t sv[kCols], dpv[kCols];
-          ptx::tmem_ld32(tmem + Cfg::kTmemST + lane_addr + wg * kCols, sv);
-          ptx::tmem_ld32(tmem + Cfg::kTmemDPT + lane_addr + wg * kCols, dpv);
-          ptx::tmem_wait_ld();
-          uint32_t pk_p[kCols / 2], pk_ds[kCols / 2];
-          if (cls == kTileMasked) {
-            const int lo = (qh == it.kh ? same_lo : cross_lo) - (qa + wg * kCols);
-            const int hi = (qh == it.kh ? same_hi : cross_hi) - (qa + wg * kCols);
-            softmax_backward_cols<kBf16, kSoftcap, true, true, true>(sv, dpv, stats + wg * kCols,
-                                                                      stats + 128 + wg * kCols, 0.f, 0.f, p.scale_log2,
-                                                                      p.softcap_pre, lo, hi, pk_p, pk_ds);
-          } else {
-            softmax_backward_cols<kBf16, kSoftcap, true, false, true>(sv, dpv, stats + wg * kCols,
-                                                                       stats + 128 + wg * kCols, 0.f, 0.f, p.scale_log2,
-                                                                       p.softcap_pre, 0, 0, pk_p, pk_ds);
-          }
-          // a warp overwrites only columns it has itself already loaded: its P^T / dS^T pieces (kCols/2 packed
-          // columns) go to the start of its own kCols columns of S^T / dP^T
-          ptx::tmem_st16(tmem + Cfg::kTmemST + lane_addr + wg * kCols, pk_p);
-          ptx::tmem_st16(tmem + Cfg::kTmemDPT + lane_addr + wg * kCols, pk_ds);
-          ptx::tmem_wait_st();
-          ptx::tc_fence_before();
-          ptx::mbar_arrive_warp(pds_full);
+      alive = for_each_substep(it, plan, spans, [&](const SubStep& st) -> bool {
+        const uint32_t u = gc & 1u, stage = gc % kStages;
+        const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * Cfg::kSubTileBytes);
+        // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
+        if (!ptx::mbar_wait(&st_full[stage], (gc / kStages) & 1u, abort_flag, 60)) return false;
+        if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) return false;
+        ++gc;
+        ptx::tc_fence_after();
+        const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
+        const uint32_t dpt_t = st_t + 64;
+        uint32_t sv[kSubCols], dpv[kSubCols];
+        ptx::tmem_ld16(st_t, sv);
+        ptx::tmem_ld16(dpt_t, dpv);
+        ptx::tmem_wait_ld();
+        uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
+        const float* l2 = stats + wg * kSubCols;
+        const float* dl = stats + kSub + wg * kSubCols;
+        if (st.cls == kTileMasked) {
+          const int lo = (st.qh == it.kh ? same_lo : cross_lo) - (st.sa + wg * kSubCols);
+          const int hi = (st.qh == it.kh ? same_hi : cross_hi) - (st.sa + wg * kSubCols);
+          softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, true, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
+                                                                              p.softcap_pre, lo, hi, pk_p, pk_ds);
+        } else {
+          softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, false, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
+                                                                               p.softcap_pre, 0, 0, pk_p, pk_ds);
         }
-      }
+        // a warp overwrites only columns it has itself already loaded: its packed P^T / dS^T pieces go to the
+        // start of its own kSubCols columns
+        ptx::tmem_st8(st_t, pk_p);
+        ptx::tmem_st8(dpt_t, pk_ds);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_warp(&pds_full[u]);
+        return true;
+      });
       if (!alive) break;
       if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
       ++n_item;
@@ -506,11 +572,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           if (gidx < kChunks) {
             const bool is_dv = gidx * 32 >= kHeadDim;
             const int col0 = gidx * 32 - (is_dv ? kHeadDim : 0);
-            uint32_t acc[32];
-            ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, acc);
+            uint32_t accv[32];
+            ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, accv);
             ptx::tmem_wait_ld();
             if (key_valid) {
-              ptx::store_row32<kBf16>(is_dv ? dv_row : dk_row, col0, acc, is_dv ? 1.f : p.softmax_scale, p.head_dim, p.wide_store != 0);
+              ptx::store_row32<kBf16>(is_dv ? dv_row : dk_row, col0, accv, is_dv ? 1.f : p.softmax_scale, p.head_dim,
+                                      p.wide_store != 0);
             }
           }
         }
@@ -568,6 +635,13 @@ template <int kHeadDim, int kStages>
 struct DqCfg {
   using T = TileCfg<kHeadDim>;
   static constexpr int kSmemBytes = (2 + kStages) * T::kTileBytes + 1024 + 512;
+  static constexpr int kKSlots = (kStages + 1) / 2 + (kStages % 2 == 0 ? 0 : 0);  // K ring; the rest is the V ring
+  static constexpr int kVSlots = kStages - kKSlots;
+  static_assert(kVSlots >= 2 && kKSlots >= 2, "ring depth");
+  __host__ __device__ static constexpr uint32_t k_slot(uint32_t step) { return step % kKSlots; }
+  __host__ __device__ static constexpr uint32_t v_slot(uint32_t step) { return kKSlots + step % kVSlots; }
+  __host__ __device__ static constexpr uint32_t k_parity(uint32_t step) { return (step / kKSlots) & 1u; }
+  __host__ __device__ static constexpr uint32_t v_parity(uint32_t step) { return (step / kVSlots) & 1u; }
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDS = 256, kTmemDQ = 384;
   static_assert(384 + kHeadDim <= 512, "tensor memory budget");
 };
@@ -644,14 +718,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           plan.step(s, kh, kt);
           if (spans.classify(kh, kt) == kTileSkip) continue;
           const int k_row = it.row0 + kh * it.n + kt * kTile;
+          // K tiles cycle through slots [0, kKSlots), V tiles through [kKSlots, kStages): a K tile is held until
+          // the dQ product of its step, a V tile only until dP, so they need rings of different depth
           for (int which = 0; which < 2; ++which) {
-            const uint32_t stage = slot % kStages;
-            if (!ptx::mbar_wait(&kv_empty[stage], ((slot / kStages) & 1) ^ 1, abort_flag, 72)) { alive = false; break; }
+            const uint32_t stage = which == 0 ? Cfg::k_slot(slot) : Cfg::v_slot(slot);
+            const uint32_t par = which == 0 ? Cfg::k_parity(slot) : Cfg::v_parity(slot);
+            if (!ptx::mbar_wait(&kv_empty[stage], par ^ 1, abort_flag, 72)) { alive = false; break; }
             ptx::mbar_expect_tx(&kv_full[stage], T::kTileBytes);
             load_tile<kHeadDim>(sKV + stage * T::kTileBytes, which == 0 ? &p.tm_k : &p.tm_v, &kv_full[stage], k_row,
                                 it.hk, it.bcoord);
-            ++slot;
           }
+          ++slot;
         }
         ++n_item;
       }
@@ -683,37 +760,37 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
         // S/dP of step j+1 are issued before dQ of step j so the tensor pipe has work during the softmax math
-        auto issue_sdp = [&](uint32_t slot_k) -> bool {
+        auto issue_sdp = [&](uint32_t step) -> bool {
+          const uint32_t ks = Cfg::k_slot(step), vs = Cfg::v_slot(step);
           if (!ptx::mbar_wait(sdp_free, (cnt_sdp & 1) ^ 1, abort_flag, 82)) return false;
           ++cnt_sdp;
-          if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 83)) return false;
-          if (!ptx::mbar_wait(&kv_full[(slot_k + 1) % kStages], ((slot_k + 1) / kStages) & 1, abort_flag, 84)) return false;
+          if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) return false;
+          if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) return false;
           ptx::tc_fence_after();
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, q_lo, kv_lo_k + (slot_k % kStages) * (T::kTileBytes >> 4), idesc_s);
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, do_lo, kv_lo_k + ((slot_k + 1) % kStages) * (T::kTileBytes >> 4),
-                                    idesc_s);
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, q_lo, kv_lo_k + ks * (T::kTileBytes >> 4), idesc_s);
+          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, do_lo, kv_lo_k + vs * (T::kTileBytes >> 4), idesc_s);
           ptx::umma_commit(sdp_full);
-          ptx::umma_commit(&kv_empty[(slot_k + 1) % kStages]);  // V tile no longer needed
+          ptx::umma_commit(&kv_empty[vs]);  // V tile no longer needed
           return true;
         };
         if (!issue_sdp(slot)) break;
         for (int j = 0; j < active && alive; ++j) {
-          const uint32_t slot_k = slot + 2 * j;
+          const uint32_t step = slot + j;
           if (j + 1 < active) {
-            if (!issue_sdp(slot_k + 2)) { alive = false; break; }
+            if (!issue_sdp(step + 1)) { alive = false; break; }
           }
           if (!ptx::mbar_wait(ds_full, cnt_ds & 1, abort_flag, 85)) { alive = false; break; }
           ++cnt_ds;
           ptx::tc_fence_after();
           mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS, kCols / 2,
-                                    kv_lo_mn + (slot_k % kStages) * (T::kTileBytes >> 4), idesc_g, j > 0);
-          ptx::umma_commit(&kv_empty[slot_k % kStages]);
+                                    kv_lo_mn + Cfg::k_slot(step) * (T::kTileBytes >> 4), idesc_g, j > 0);
+          ptx::umma_commit(&kv_empty[Cfg::k_slot(step)]);
           ptx::umma_commit(ds_free);
         }
         if (!alive) break;
         ptx::umma_commit(q_empty);
         ptx::umma_commit(dq_full);
-        slot += 2 * active;
+        slot += active;
         ++n_item;
       }
     }
@@ -762,10 +839,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         ptx::mbar_arrive_warp(sdp_free);
         uint32_t pk_ds[kCols / 2];
         if (cls == kTileMasked) {
-          softmax_backward_cols<kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
+          softmax_backward_cols<kCols, kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
                                                                       p.softcap_pre, lo, hi, nullptr, pk_ds);
         } else {
-          softmax_backward_cols<kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
+          softmax_backward_cols<kCols, kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
                                                                        p.softcap_pre, 0, 0, nullptr, pk_ds);
         }
         if (!ptx::mbar_wait(ds_free, (cnt & 1) ^ 1, abort_flag, 92)) { alive = false; break; }
@@ -884,6 +961,12 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   rc = encode_tile_map(&p.tm_do, a.dout.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.dout.row_stride,
                        a.dout.head_stride, a.dout.batch_stride, 64, kTile);
   if (rc) return rc;
+  rc = encode_tile_map(&p.tm_q64, a.q.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.q.row_stride,
+                       a.q.head_stride, a.q.batch_stride, 64, kSub);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_do64, a.dout.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.dout.row_stride,
+                       a.dout.head_stride, a.dout.batch_stride, 64, kSub);
+  if (rc) return rc;
   rc = encode_tile_map(&p.tm_k, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
                        a.k.head_stride, a.k.batch_stride, 64, kTile);
   if (rc) return rc;
@@ -966,8 +1049,8 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
     }
     FDA_CUDA_TRY(cudaGetLastError());
   }
-  if (d_round == 64) return dispatch_bwd<64, 3, 6>(p, sm_count, bf16, softcap, stage_mask, stream);
-  return dispatch_bwd<128, 2, 4>(p, sm_count, bf16, softcap, stage_mask, stream);
+  if (d_round == 64) return dispatch_bwd<64, 6, 7>(p, sm_count, bf16, softcap, stage_mask, stream);
+  return dispatch_bwd<128, 4, 5>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
 #ifdef FDA_WAIT_CLOCKS

@@ -104,7 +104,7 @@ namespace ptx {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
   const long long t0 = clock64();
   const bool ok = mbar_wait_impl(bar, parity, abort_flag, code);
-  if ((threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x >= 256)) {
+  if ((threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x + 64 >= blockDim.x)) {
     atomicAdd(&g_fda_wait[code & 127], static_cast<unsigned long long>(clock64() - t0));
     atomicAdd(&g_fda_wait[128 + (code & 127)], 1ull);
   }

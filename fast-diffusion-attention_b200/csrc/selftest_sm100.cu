@@ -19,6 +19,9 @@ struct SelfTestParams {
 };
 
 constexpr int kPanelBytes = 128 * 128;  // [128 rows][64 bf16]
+#ifdef FDA_UMMA_TIMING
+__device__ long long g_umma_timing[8];
+#endif
 
 __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_constant__ SelfTestParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -26,6 +29,10 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
   uint8_t* sA = smem;                    // up to 2 panels
   uint8_t* sB = smem + 2 * kPanelBytes;  // up to 4 panels (mode 1: [k rows][64 cols] x n/64; mode 0: [n rows][64] x k/64)
   __shared__ uint64_t bar_load, bar_mma;
+#ifdef FDA_UMMA_TIMING
+  __shared__ uint64_t bar_time, bar_mma2, bar_w1;
+  __shared__ int go_flag;
+#endif
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_flag;
 
@@ -34,6 +41,12 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
     abort_flag = 0;
     ptx::mbar_init(&bar_load, 1);
     ptx::mbar_init(&bar_mma, 1);
+#ifdef FDA_UMMA_TIMING
+    ptx::mbar_init(&bar_time, 1);
+    ptx::mbar_init(&bar_w1, 1);
+    go_flag = 0;
+    ptx::mbar_init(&bar_mma2, 1);
+#endif
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
@@ -103,8 +116,91 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
       }
     }
     ptx::umma_commit(&bar_mma);
+#ifdef FDA_UMMA_TIMING
+    // Debug build only: issue cost and execution time of a burst of identical MMAs (the accumulator is junk after).
+    ptx::mbar_wait(&bar_mma, 0, &abort_flag, 103);
+    {
+      constexpr int kBurst = 256;
+      const uint32_t a_lo = ptx::smem_desc_lo(ptx::smem_u32(sA), 16);
+      const uint32_t b_lo = ptx::smem_desc_lo(ptx::smem_u32(sB), p.mode == 0 ? 16 : p.k * 128);
+      const uint32_t idesc = ptx::make_idesc(128, p.n, 1, false, p.mode != 0);
+      const uint32_t idesc_ss128 = ptx::make_idesc(128, 128, 1, false, false);
+      const long long t0 = clock64();
+      for (int i = 0; i < kBurst; ++i) {
+        if (p.mode == 0) ptx::umma_ss_f16_lh(tmem_c, a_lo + (i & 3) * 2, b_lo + (i & 3) * 2, ptx::smem_desc_hi(1024), idesc, 1);
+        else ptx::umma_ts_f16_lh(tmem_c, tmem_a + (i & 3) * 8, b_lo + (i & 3) * 128, ptx::smem_desc_hi(1024), idesc, 1);
+      }
+      const long long t1 = clock64();
+      ptx::umma_commit(&bar_time);
+      ptx::mbar_wait(&bar_time, 0, &abort_flag, 104);
+      const long long t2 = clock64();
+      g_umma_timing[0] = kBurst;
+      g_umma_timing[1] = t1 - t0;
+      g_umma_timing[2] = t2 - t0;
+      // unrolled burst without per-iteration branches
+      const uint32_t hi = ptx::smem_desc_hi(1024);
+      const long long u0 = clock64();
+      if (p.mode == 0) {
+#pragma unroll 1
+        for (int i = 0; i < kBurst; i += 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ptx::umma_ss_f16_lh(tmem_c, a_lo + (j & 3) * 2, b_lo + (j & 3) * 2, hi, idesc, 1);
+        }
+      } else {
+#pragma unroll 1
+        for (int i = 0; i < kBurst; i += 8) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ptx::umma_ts_f16_lh(tmem_c, tmem_a + (j & 3) * 8, b_lo + (j & 3) * 128, hi, idesc, 1);
+        }
+      }
+      const long long u1 = clock64();
+      ptx::umma_commit(&bar_time);
+      ptx::mbar_wait(&bar_time, 1, &abort_flag, 107);
+      g_umma_timing[4] = u1 - u0;
+      g_umma_timing[5] = clock64() - u0;
+      // two issuing threads: signal warp 1 to issue the same burst into other columns at the same time
+      *reinterpret_cast<volatile int*>(&go_flag) = 1;
+      const long long w0 = clock64();
+#pragma unroll 1
+      for (int i = 0; i < kBurst; i += 8) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ptx::umma_ss_f16_lh(tmem_c, a_lo + (j & 3) * 2, b_lo + (j & 3) * 2, hi, idesc_ss128, 1);
+      }
+      ptx::umma_commit(&bar_time);
+      ptx::mbar_wait(&bar_time, 0, &abort_flag, 108);
+      ptx::mbar_wait(&bar_w1, 0, &abort_flag, 109);
+      g_umma_timing[6] = clock64() - w0;
+      // latency of one MMA + commit + wait round trip
+      const long long t3 = clock64();
+      if (p.mode == 0) ptx::umma_ss_f16_lh(tmem_c, a_lo, b_lo, ptx::smem_desc_hi(1024), idesc, 1);
+      else ptx::umma_ts_f16_lh(tmem_c, tmem_a, b_lo, ptx::smem_desc_hi(1024), idesc, 1);
+      ptx::umma_commit(&bar_time);
+      ptx::mbar_wait(&bar_time, 1, &abort_flag, 105);
+      g_umma_timing[3] = clock64() - t3;
+      ptx::umma_commit(&bar_mma2);
+    }
+#endif
   }
+#ifdef FDA_UMMA_TIMING
+  if (threadIdx.x == 32) {
+    long long spin0 = clock64();
+    while (*reinterpret_cast<volatile int*>(&go_flag) == 0 && clock64() - spin0 < 2000000000LL) {}
+    const uint32_t a_lo = ptx::smem_desc_lo(ptx::smem_u32(sA), 16);
+    const uint32_t b_lo = ptx::smem_desc_lo(ptx::smem_u32(sB), 16);
+    const uint32_t idesc_ss128 = ptx::make_idesc(128, 128, 1, false, false);
+    const uint32_t hi = ptx::smem_desc_hi(1024);
+#pragma unroll 1
+    for (int i = 0; i < 256; i += 8) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ptx::umma_ss_f16_lh(tmem + 384, a_lo + (j & 3) * 2, b_lo + (j & 3) * 2, hi, idesc_ss128, 1);
+    }
+    ptx::umma_commit(&bar_w1);
+  }
+#endif
   ptx::mbar_wait(&bar_mma, 0, &abort_flag, 102);
+#ifdef FDA_UMMA_TIMING
+  ptx::mbar_wait(&bar_mma2, 0, &abort_flag, 106);
+#endif
   ptx::tc_fence_after();
   {
     const int row = warp * 32 + lane;
@@ -156,6 +252,12 @@ int launch_selftest_umma(int mode, const void* a, const void* b, float* c, int n
   FDA_CUDA_TRY(cudaGetLastError());
   return FDA_OK;
 }
+
+#ifdef FDA_UMMA_TIMING
+extern "C" int fda_debug_umma_timing(long long* out8) {
+  return cudaMemcpyFromSymbol(out8, g_umma_timing, sizeof(long long) * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int read_status_selftest(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};
