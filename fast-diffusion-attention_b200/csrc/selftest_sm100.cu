@@ -217,7 +217,100 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
   if (warp == 0) ptx::tmem_dealloc(tmem, 512);
 }
 
+#ifdef FDA_UMMA_TIMING
+// Debug build only: cost of a burst of MMAs issued by one thread of warp 16 while warps 0-15 make "noise" of one
+// kind: 0 idle (parked on a barrier), 1 polling an mbarrier that never completes, 2 FMA + ex2 arithmetic,
+// 3 shared-memory loads. out[noise] = cycles per MMA for SS N=128, out[4 + noise] for SS N=64, out[8 + noise] TS.
+__device__ long long g_contention[32];
+__global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar_never, bar_done;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int stop_flag, abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    stop_flag = 0; abort_flag = 0;
+    ptx::mbar_init(&bar_never, 1);
+    ptx::mbar_init(&bar_done, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 16) { ptx::tmem_alloc(&tmem_base_s, 512); ptx::tmem_relinquish(); }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  volatile int* stop = &stop_flag;
+  if (warp < 16) {
+    float acc = static_cast<float>(threadIdx.x);
+    if (noise == 1) {
+      while (!*stop) { if (ptx::mbar_try_wait(&bar_never, 0)) break; }
+    } else if (noise == 2) {
+      while (!*stop) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc = ptx::ex2(fmaf(acc, 0.5f, -1.f)) + acc * 0.25f;
+      }
+    } else if (noise == 3) {
+      const float4* src = reinterpret_cast<const float4*>(smem) + (threadIdx.x & 255);
+      while (!*stop) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float4 v = src[i * 512]; acc += v.x + v.w; }
+      }
+    }
+    else if (noise >= 4) {
+      const uint32_t taddr = tmem + 384 + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+      uint32_t r[32];
+      while (!*stop) {
+        ptx::tmem_ld32(taddr, r);
+        ptx::tmem_wait_ld();
+        if (noise == 5) { ptx::tmem_st32(taddr + 32, r); ptx::tmem_wait_st(); }
+        acc += __uint_as_float(r[lane]);
+      }
+    }
+    if (acc == 123.456f) g_contention[15] = 1;
+  } else if (lane == 0) {
+    constexpr int kBurst = 256;
+    const uint32_t hi = ptx::smem_desc_hi(1024);
+    const uint32_t a_lo = ptx::smem_desc_lo(ptx::smem_u32(smem), 16);
+    const uint32_t b_lo = ptx::smem_desc_lo(ptx::smem_u32(smem + 32768), 16);
+    const uint32_t b_mn = ptx::smem_desc_lo(ptx::smem_u32(smem + 32768), 16384);
+    for (int variant = 0; variant < 3; ++variant) {
+      const uint32_t idesc = variant == 0 ? ptx::make_idesc(128, 128, 1, false, false)
+                                          : (variant == 1 ? ptx::make_idesc(128, 64, 1, false, false)
+                                                          : ptx::make_idesc(128, 128, 1, false, true));
+      const long long t0 = clock64();
+#pragma unroll 1
+      for (int i = 0; i < kBurst; i += 8) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (variant < 2) ptx::umma_ss_f16_lh(tmem, a_lo + (j & 3) * 2, b_lo + (j & 3) * 2, hi, idesc, 1);
+          else ptx::umma_ts_f16_lh(tmem, tmem + 256 + (j & 3) * 8, b_mn + (j & 3) * 128, hi, idesc, 1);
+        }
+      }
+      ptx::umma_commit(&bar_done);
+      ptx::mbar_wait(&bar_done, variant & 1, &abort_flag, 110);
+      g_contention[variant * 8 + noise] = (clock64() - t0) / kBurst;
+    }
+    *stop = 1;
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 16) ptx::tmem_dealloc(tmem, 512);
+}
+#endif
+
 }  // namespace
+
+#ifdef FDA_UMMA_TIMING
+extern "C" int fda_debug_umma_contention(long long* out16) {
+  cudaFuncSetAttribute(umma_contention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  for (int noise = 0; noise < 6; ++noise) {
+    umma_contention_kernel<<<1, 544, 200 * 1024>>>(noise);
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  }
+  return cudaMemcpyFromSymbol(out16, g_contention, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 int launch_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, cudaStream_t stream) {
   if (!a || !b || !c) return FDA_ERR_NULL;
