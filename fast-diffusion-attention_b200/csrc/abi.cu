@@ -65,6 +65,19 @@ int fda_bwd_stages(const FdaBwdArgs* a, unsigned stage_mask, void* stream) {
 
 int fda_bwd(const FdaBwdArgs* a, void* stream) { return fda_bwd_stages(a, 7u, stream); }
 
+// Same checks as fda_bwd except for the workspace, which this variant does not take from the caller.
+int fda_bwd_noalloc(const FdaBwdArgs* a, void* stream) {
+  if (!a) return FDA_ERR_NULL;
+  int rc = fda::check_problem(a->p, true);
+  if (rc) return rc;
+  if (a->p.total == 0 || a->p.batch == 0) return FDA_OK;
+  if (!a->q.ptr || !a->k.ptr || !a->v.ptr || !a->out.ptr || !a->dout.ptr || !a->dq.ptr || !a->dk.ptr ||
+      !a->dv.ptr || !a->lse) {
+    return FDA_ERR_NULL;
+  }
+  return fda::launch_bwd_noalloc(*a, static_cast<cudaStream_t>(stream));
+}
+
 const char* fda_strerror(int status) {
   switch (status) {
     case FDA_OK: return "success";
@@ -85,6 +98,9 @@ const char* fda_strerror(int status) {
     case FDA_ERR_UNSUPPORTED: return "this feature combination is not built";
     case FDA_ERR_SHAPE: return "inconsistent tensor sizes";
     case FDA_ERR_DEVICE_WAIT: return "a bounded device-side wait expired";
+    case FDA_ERR_SCRATCH_LIMIT:
+      return "problem too large for the built-in scratch of fda_bwd_noalloc (FDA_NOALLOC_SCRATCH_BYTES); use fda_bwd "
+             "with a caller-provided workspace";
     default: return "unknown status";
   }
 }

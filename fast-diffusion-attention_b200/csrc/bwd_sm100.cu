@@ -1062,6 +1062,31 @@ extern "C" int fda_debug_waits_bwd(unsigned long long* out256) {
 }
 #endif
 
+// ------------------------------------------------------------------------------------------------------------
+// Backward without a caller-provided workspace (fda_bwd_noalloc). The scratch the three kernels share (delta,
+// LSE * log2(e), the two work counters) lives in this fixed array, which every GPU that loads the library holds
+// until the process exits. In host code the array's name is only a stand-in for the symbol: the device address
+// is looked up once per device, with that device current, and that pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_bwd_noalloc_scratch[FDA_NOALLOC_SCRATCH_BYTES];
+
+int launch_bwd_noalloc(const FdaBwdArgs& a, cudaStream_t stream) {
+  if (bwd_workspace_bytes(a.p) > static_cast<size_t>(FDA_NOALLOC_SCRATCH_BYTES)) return FDA_ERR_SCRATCH_LIMIT;
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  FDA_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FDA_ERR_UNSUPPORTED;
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    FDA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_bwd_noalloc_scratch));
+    scratch_of_device[dev] = ptr;
+  }
+  FdaBwdArgs with_scratch = a;
+  with_scratch.workspace = scratch_of_device[dev];
+  with_scratch.workspace_bytes = FDA_NOALLOC_SCRATCH_BYTES;
+  return launch_bwd(with_scratch, stream, 7u);
+}
+
 int read_status_bwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};
   FDA_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_fda_status, sizeof(int) * 4));

@@ -15,6 +15,8 @@ FDA_BF16, FDA_FP16, FDA_E4M3 = 0, 1, 2
 
 FDA_OK = 0
 FDA_ERR_DEVICE_WAIT = 14
+FDA_ERR_SCRATCH_LIMIT = 15
+NOALLOC_SCRATCH_BYTES = 16 << 20
 
 
 class FdaTensor(C.Structure):
@@ -44,7 +46,7 @@ class FdaBwdArgs(C.Structure):
 
 
 EXPORTS = [
-    "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_bwd_stages", "fda_strerror",
+    "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_bwd_stages", "fda_bwd_noalloc", "fda_strerror",
     "fda_last_cuda_error", "fda_device_status", "fda_version", "fda_geom_key_plan", "fda_geom_query_plan",
     "fda_geom_classify", "fda_selftest_umma",
 ]
@@ -72,6 +74,8 @@ def load():
     lib.fda_bwd.argtypes = [C.POINTER(FdaBwdArgs), C.c_void_p]
     lib.fda_bwd_stages.restype = C.c_int
     lib.fda_bwd_stages.argtypes = [C.POINTER(FdaBwdArgs), C.c_uint, C.c_void_p]
+    lib.fda_bwd_noalloc.restype = C.c_int
+    lib.fda_bwd_noalloc.argtypes = [C.POINTER(FdaBwdArgs), C.c_void_p]
     lib.fda_strerror.restype = C.c_char_p
     lib.fda_strerror.argtypes = [C.c_int]
     lib.fda_last_cuda_error.restype = C.c_char_p

@@ -41,7 +41,8 @@ typedef enum FdaStatus {
   FDA_ERR_ARCH = 11,           /* the current device is not sm_100 */
   FDA_ERR_UNSUPPORTED = 12,    /* feature combination not built */
   FDA_ERR_SHAPE = 13,          /* inconsistent sizes */
-  FDA_ERR_DEVICE_WAIT = 14     /* a bounded device-side wait expired (reported by fda_device_status) */
+  FDA_ERR_DEVICE_WAIT = 14,    /* a bounded device-side wait expired (reported by fda_device_status) */
+  FDA_ERR_SCRATCH_LIMIT = 15   /* fda_bwd_noalloc: the problem needs more scratch than the built-in array holds */
 } FdaStatus;
 
 typedef enum FdaDtype { FDA_BF16 = 0, FDA_FP16 = 1, FDA_E4M3 = 2 } FdaDtype;
@@ -111,6 +112,26 @@ int fda_bwd(const FdaBwdArgs* args, void* stream);
  * stages read what the preprocess left in the workspace. For profiling and per-kernel timing; the reference
  * has the same stages as separate launches (csrc/fda/flash_bwd_launch_template.h:47-239). */
 int fda_bwd_stages(const FdaBwdArgs* args, unsigned stage_mask, void* stream);
+
+/* Backward pass for callers that cannot hand the library a workspace. Some hosts of this library own no device
+ * allocator at the point of the call: a serving process whose device memory was carved up at start-up and that
+ * forbids allocator calls on its request path, a host language binding that reaches CUDA only through this ABI,
+ * or a training loop that runs under a memory plan fixed ahead of time. For them fda_bwd is unusable because it
+ * needs fda_bwd_workspace_bytes() of caller-provided scratch. This entry point takes the same arguments but
+ * ignores args->workspace / args->workspace_bytes: the per-row statistics and the two work counters live in a
+ * fixed array of FDA_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU that loads it (it is
+ * held until the process exits). The caller still provides every input and output tensor.
+ *  - Problems whose scratch need exceeds the array (batch * heads * round_up(n, 128) * 16 bytes + 512) are
+ *    rejected with FDA_ERR_SCRATCH_LIMIT; nothing is launched.
+ *  - It never calls cudaMalloc / cudaFree or any allocating routine. The first call on a device looks up the
+ *    device address of the array (cudaGetSymbolAddress) with that device current; make that first call outside
+ *    of any stream capture.
+ *  - All calls share the one array: two calls whose kernels may overlap on the GPU (different streams, no
+ *    ordering between them) race on it. Calls on one stream are safe; each call rewrites what it reads and
+ *    re-zeroes the counters itself, so stale contents of an earlier call do not matter.
+ * It has no counterpart in the reference, whose operator allocates its workspaces with torch inside the call. */
+#define FDA_NOALLOC_SCRATCH_BYTES (16u << 20)
+int fda_bwd_noalloc(const FdaBwdArgs* args, void* stream);
 
 /* Message for a status code. */
 const char* fda_strerror(int status);
