@@ -37,6 +37,11 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch on this workload, from the ncu capture summarised in
+# profiles/c2_step_kernels_ncu.md (bytes)
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 526.3e6, "bwd_dkdv_kernel": 803.9e6, "bwd_dq_kernel": 661.9e6,
+                     "bwd_preprocess_kernel": None}
+
 WORKLOAD = dict(name="C2 bf16 MHA fwd+bwd", batch=8, n=2048, heads=16, heads_k=16, head_dim=128, block_size=256)
 METRIC = "train-step TFLOPS (visible pairs), bf16 d=128"
 
@@ -250,7 +255,8 @@ def main():
     peaks = measured_peaks()
     achieved = algorithmic[top] / (kernel_ms[top] * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel=names[top], achieved=achieved, peak=peaks["tflops_sustained"],
-                    unit="TFLOP/s", frac=achieved / peaks["tflops_sustained"], traffic=None,
+                    unit="TFLOP/s", frac=achieved / peaks["tflops_sustained"], traffic=NCU_TRAFFIC_BYTES.get(names[top]),
+                    traffic_unit="bytes per launch (ncu dram read + write, profiles/c2_step_kernels_ncu.md)",
                     peak_source=peaks["source"] + " cuBLAS bf16, sustained (kernel timed inside a long step)",
                     kernel_ms={nm: round(ms, 4) for nm, ms in zip(names, kernel_ms)},
                     kernel_tflops_algorithmic={nm: (round(f / (ms * 1e-3) / 1e12, 1) if f else None)
