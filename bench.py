@@ -57,28 +57,66 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons (read-only NVML queries, nvidia-smi as a fallback) while the timed
+    region runs."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
-        self.samples = []
+        self.mhz, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if visible:
+                ids = [x.strip() for x in visible.split(",") if x.strip()]
+                if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                    phys = int(ids[gpu_index])
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        self.mhz.append(float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)))
+        try:
+            mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+        except Exception:
+            mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        for name, bit in self.REASON_BITS.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
+        out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
+                              "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+        parts = [x.strip() for x in out.stdout.strip().split(",")]
+        if len(parts) >= 6 and parts[0].replace(".", "").isdigit():
+            self.mhz.append(float(parts[0]))
+            self.max_mhz = float(parts[1]) if parts[1].replace(".", "").isdigit() else self.max_mhz
+            for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
+                if parts[2 + i].lower().startswith("active"):
+                    self.reasons.add(name)
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.QUERY,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                parts = [x.strip() for x in out.stdout.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.002 if self._nvml is not None else 0.05)
 
     def __enter__(self):
         self._thread.start()
@@ -89,14 +127,10 @@ class ClockSampler:
         self._thread.join(timeout=6)
 
     def summary(self):
-        if not self.samples:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unsampled"])
-        mhz = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [nm for i, nm in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return dict(sm_mhz=statistics.median(mhz) if mhz else None,
-                    sm_max_mhz=float(self.samples[0][1]) if self.samples[0][1].replace(".", "").isdigit() else None,
-                    reasons=reasons, samples=len(self.samples))
+        if not self.mhz:
+            return dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=["unsampled"])
+        return dict(sm_mhz=statistics.median(self.mhz), sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons),
+                    samples=len(self.mhz), source="nvml" if self._nvml is not None else "nvidia-smi")
 
 
 def make_cpu_sample(threads=None):
@@ -159,7 +193,7 @@ def run_reference_arm(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu-baseline", action="store_true")

@@ -36,6 +36,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct BwdParams {
   CUtensorMap tm_q, tm_k, tm_v, tm_do;
   CUtensorMap tm_q64, tm_do64;  // same tensors, 64-row boxes (dK/dV kernel)
+  CUtensorMap tm_k64, tm_v64;   // 64-row boxes of K / V (dQ kernel for head dimensions above 128)
   const void* out;
   const void* dout;
   void* dq;
@@ -294,8 +295,13 @@ struct DkdvCfg {
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
   static constexpr int kThreads = kBwdThreads;
   // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
-  static constexpr int kTmemDK = 256, kTmemDV = 256 + kHeadDim;
-  static_assert(256 + 2 * kHeadDim <= 512, "tensor memory budget");
+  // head dimensions above 128 do not leave room for both accumulators next to the S^T / dP^T buffers: the key
+  // tile is then processed in kPasses passes, each producing kAccDim columns of dK and dV
+  static constexpr int kAccDim = kHeadDim > 128 ? 128 : kHeadDim;
+  static constexpr int kPasses = kHeadDim / kAccDim;
+  static constexpr int kLookahead = kStages >= 2 ? 2 : 1;  // S^T / dP^T sub-steps issued ahead of dV / dK
+  static constexpr int kTmemDK = 256, kTmemDV = 256 + kAccDim;
+  static_assert(256 + 2 * kAccDim <= 512, "tensor memory budget");
   static_assert(kStageBytes % 1024 == 0, "sub-tiles must stay 1024-byte aligned for the 128-byte swizzle");
 };
 
@@ -353,7 +359,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   const uint32_t tmem = *tmem_slot;
   const int bs = p.block_size;
   const int group = p.heads / p.heads_k;
-  const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+  const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch * Cfg::kPasses;
 
   // Calls fn(SubStep) for every non-skipped sub-step of the item, in order; stops early when fn returns false.
   auto for_each_substep = [&](const KvItem& it, const QueryPlan& plan, const KvSpans& spans, auto&& fn) -> bool {
@@ -388,7 +394,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_produce(mbox, n_sched, p.ticket_kv, abort_flag);
         if (idx < 0 || idx >= total_items) break;
-        const KvItem it = decode_kv_item(p, idx);
+        const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
         if (!it.valid) continue;
         const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
         const KvSpans spans = make_kv_spans(it, bs);
@@ -424,8 +430,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, kSub, kFmt, false, false);
-      const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      const uint32_t idesc_g = ptx::make_idesc(kTile, Cfg::kAccDim, kFmt, false, true);
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
+      uint32_t pass_panel_off = 0;  // descriptor offset of the first 64-column panel of this pass in a sub-tile
       const uint32_t k_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t v_lo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
       const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);                      // K-major use
@@ -444,12 +451,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         const uint32_t st_t = tmem + u * 128, dpt_t = tmem + u * 128 + 64;
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk) {
-          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols, st_lo_mn + do_off + kk * (2048 >> 4), kHi, idesc_g,
+          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols,
+                              st_lo_mn + do_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
                               (acc || kk > 0) ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < kSub / 16; ++kk) {
-          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDK, dpt_t + kk * kSubCols, st_lo_mn + q_off + kk * (2048 >> 4), kHi, idesc_g,
+          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDK, dpt_t + kk * kSubCols,
+                              st_lo_mn + q_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
                               (acc || kk > 0) ? 1u : 0u);
         }
         acc = true;
@@ -461,14 +470,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
         if (idx < 0 || idx >= total_items) break;
-        const KvItem it = decode_kv_item(p, idx);
+        const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
         if (!it.valid) continue;
         const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
         const KvSpans spans = make_kv_spans(it, bs);
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
         acc = false;
+        pass_panel_off = (idx % Cfg::kPasses) * (Cfg::kAccDim / 64) * (Cfg::kSubPanelBytes >> 4);
         alive = for_each_substep(it, plan, spans, [&](const SubStep&) -> bool {
-          if (g_issued - g_done == 2) {
+          if (g_issued - g_done == Cfg::kLookahead) {
             if (!retire()) return false;
           }
           const uint32_t u = g_issued & 1u, stage = g_issued % kStages;
@@ -510,7 +520,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     for (uint32_t n_sched = 0; alive; ++n_sched) {
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
       if (idx < 0 || idx >= total_items) break;
-      const KvItem it = decode_kv_item(p, idx);
+      const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
+      const int pass_col0 = (idx % Cfg::kPasses) * Cfg::kAccDim;
       if (!it.valid) continue;
       const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
       const KvSpans spans = make_kv_spans(it, bs);
@@ -565,13 +576,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         uint16_t* dv_row = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
         // dK and dV sit side by side in tensor memory: 2 * d / 32 chunks of 32 columns, dealt round-robin to the
         // compute warpgroups
-        constexpr int kChunks = 2 * kHeadDim / 32;
+        constexpr int kChunks = 2 * Cfg::kAccDim / 32;
 #pragma unroll
         for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
           const int gidx = g0 + wg;
           if (gidx < kChunks) {
-            const bool is_dv = gidx * 32 >= kHeadDim;
-            const int col0 = gidx * 32 - (is_dv ? kHeadDim : 0);
+            const bool is_dv = gidx * 32 >= Cfg::kAccDim;
+            const int col0 = pass_col0 + gidx * 32 - (is_dv ? Cfg::kAccDim : 0);
             uint32_t accv[32];
             ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, accv);
             ptx::tmem_wait_ld();
@@ -621,7 +632,7 @@ __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
 
 struct QSpans {
   Span half[2];  // key spans of the query tile per key half (0 noisy, 1 clean)
-  __device__ __forceinline__ int classify(int kh, int kt) const { return half[kh].classify(kt * kTile, kTile); }
+  __device__ __forceinline__ int classify(int kh, int k0, int keys) const { return half[kh].classify(k0, keys); }
 };
 
 __device__ __forceinline__ QSpans make_q_spans(const QItem& it, int bs) {
@@ -634,16 +645,21 @@ __device__ __forceinline__ QSpans make_q_spans(const QItem& it, int bs) {
 template <int kHeadDim, int kStages>
 struct DqCfg {
   using T = TileCfg<kHeadDim>;
-  static constexpr int kSmemBytes = (2 + kStages) * T::kTileBytes + 1024 + 512;
-  static constexpr int kKSlots = (kStages + 1) / 2 + (kStages % 2 == 0 ? 0 : 0);  // K ring; the rest is the V ring
+  // keys per step: 128, or 64 for head dimensions above 128 (Q and dO alone take 128 KB of shared memory there)
+  static constexpr int kKeys = kHeadDim > 128 ? 64 : 128;
+  static constexpr int kKeyCols = kKeys / kCmpWG;               // key columns per compute warpgroup
+  static constexpr int kKvTileBytes = kKeys * kHeadDim * 2;
+  static constexpr int kKvPanelBytes = kKeys * 128;
+  static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kKvTileBytes + 1024 + 512;
+  static constexpr int kKSlots = (kStages + 1) / 2;  // K ring; the rest is the V ring
   static constexpr int kVSlots = kStages - kKSlots;
-  static_assert(kVSlots >= 2 && kKSlots >= 2, "ring depth");
+  static_assert(kVSlots >= 1 && kKSlots >= 2, "ring depth");
   __host__ __device__ static constexpr uint32_t k_slot(uint32_t step) { return step % kKSlots; }
   __host__ __device__ static constexpr uint32_t v_slot(uint32_t step) { return kKSlots + step % kVSlots; }
   __host__ __device__ static constexpr uint32_t k_parity(uint32_t step) { return (step / kKSlots) & 1u; }
   __host__ __device__ static constexpr uint32_t v_parity(uint32_t step) { return (step / kVSlots) & 1u; }
-  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDS = 256, kTmemDQ = 384;
-  static_assert(384 + kHeadDim <= 512, "tensor memory budget");
+  static constexpr int kTmemS = 0, kTmemDP = kKeys, kTmemDS = 2 * kKeys, kTmemDQ = kHeadDim > 128 ? 256 : 384;
+  static_assert(kTmemDQ + kHeadDim <= 512 && 2 * kKeys + kKeys / 2 <= kTmemDQ, "tensor memory budget");
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
@@ -655,7 +671,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   uint8_t* sQ = smem;
   uint8_t* sdO = smem + T::kTileBytes;
   uint8_t* sKV = smem + 2 * T::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * T::kTileBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * Cfg::kKvTileBytes);
   uint64_t* q_full = bars;
   uint64_t* q_empty = bars + 1;
   uint64_t* kv_full = bars + 2;
@@ -706,7 +722,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         if (idx < 0 || idx >= total_items) break;
         const QItem it = decode_q_item(p, idx);
         if (!it.valid) continue;
-        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
         const QSpans spans = make_q_spans(it, bs);
         if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 71)) break;
         ptx::mbar_expect_tx(q_full, 2 * T::kTileBytes);
@@ -716,17 +732,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         for (int s = 0; s < plan.steps() && alive; ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
-          if (spans.classify(kh, kt) == kTileSkip) continue;
-          const int k_row = it.row0 + kh * it.n + kt * kTile;
+          if (spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) == kTileSkip) continue;
+          const int k_row = it.row0 + kh * it.n + kt * Cfg::kKeys;
           // K tiles cycle through slots [0, kKSlots), V tiles through [kKSlots, kStages): a K tile is held until
           // the dQ product of its step, a V tile only until dP, so they need rings of different depth
           for (int which = 0; which < 2; ++which) {
             const uint32_t stage = which == 0 ? Cfg::k_slot(slot) : Cfg::v_slot(slot);
             const uint32_t par = which == 0 ? Cfg::k_parity(slot) : Cfg::v_parity(slot);
             if (!ptx::mbar_wait(&kv_empty[stage], par ^ 1, abort_flag, 72)) { alive = false; break; }
-            ptx::mbar_expect_tx(&kv_full[stage], T::kTileBytes);
-            load_tile<kHeadDim>(sKV + stage * T::kTileBytes, which == 0 ? &p.tm_k : &p.tm_v, &kv_full[stage], k_row,
-                                it.hk, it.bcoord);
+            ptx::mbar_expect_tx(&kv_full[stage], Cfg::kKvTileBytes);
+            const CUtensorMap* tm = Cfg::kKeys == 128 ? (which == 0 ? &p.tm_k : &p.tm_v)
+                                                      : (which == 0 ? &p.tm_k64 : &p.tm_v64);
+#pragma unroll
+            for (int c = 0; c < T::kPanels; ++c) {
+              ptx::tma_load_4d(sKV + stage * Cfg::kKvTileBytes + c * Cfg::kKvPanelBytes, tm, &kv_full[stage], c * 64,
+                               k_row, it.hk, it.bcoord);
+            }
           }
           ++slot;
         }
@@ -737,12 +758,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   } else if (warp == kMmaWarpB) {
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
-      const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
+      const uint32_t idesc_s = ptx::make_idesc(kTile, Cfg::kKeys, kFmt, false, false);
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
       const uint32_t q_lo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
       const uint32_t do_lo = ptx::smem_desc_lo(ptx::smem_u32(sdO), 16);
       const uint32_t kv_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sKV), 16);
-      const uint32_t kv_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV), T::kPanelBytes);
+      const uint32_t kv_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV), Cfg::kKvPanelBytes);
       uint32_t n_item = 0, slot = 0, cnt_sdp = 0, cnt_ds = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -750,13 +772,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         if (idx < 0 || idx >= total_items) break;
         const QItem it = decode_q_item(p, idx);
         if (!it.valid) continue;
-        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
         const QSpans spans = make_q_spans(it, bs);
         int active = 0;
         for (int s = 0; s < plan.steps(); ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
-          active += spans.classify(kh, kt) != kTileSkip;
+          active += spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) != kTileSkip;
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
         // S/dP of step j+1 are issued before dQ of step j so the tensor pipe has work during the softmax math
@@ -767,8 +789,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) return false;
           if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) return false;
           ptx::tc_fence_after();
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemS, q_lo, kv_lo_k + ks * (T::kTileBytes >> 4), idesc_s);
-          mma_rows_x_rows<kHeadDim>(tmem + Cfg::kTmemDP, do_lo, kv_lo_k + vs * (T::kTileBytes >> 4), idesc_s);
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            const uint32_t b_off = ((kk / 4) * Cfg::kKvPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS, q_lo + a_off, kv_lo_k + ks * (Cfg::kKvTileBytes >> 4) + b_off, kHi,
+                                idesc_s, kk > 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            const uint32_t b_off = ((kk / 4) * Cfg::kKvPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDP, do_lo + a_off, kv_lo_k + vs * (Cfg::kKvTileBytes >> 4) + b_off, kHi,
+                                idesc_s, kk > 0);
+          }
           ptx::umma_commit(sdp_full);
           ptx::umma_commit(&kv_empty[vs]);  // V tile no longer needed
           return true;
@@ -782,8 +816,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           if (!ptx::mbar_wait(ds_full, cnt_ds & 1, abort_flag, 85)) { alive = false; break; }
           ++cnt_ds;
           ptx::tc_fence_after();
-          mma_tmem_x_tile<kHeadDim>(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS, kCols / 2,
-                                    kv_lo_mn + Cfg::k_slot(step) * (T::kTileBytes >> 4), idesc_g, j > 0);
+          // dQ += dS K: the packed dS pieces of the compute warpgroups lie side by side, 8 columns per 16 keys
+#pragma unroll
+          for (int kk = 0; kk < Cfg::kKeys / 16; ++kk) {
+            ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS + kk * 8,
+                                kv_lo_mn + Cfg::k_slot(step) * (Cfg::kKvTileBytes >> 4) + kk * (2048 >> 4), kHi, idesc_g,
+                                (j > 0 || kk > 0) ? 1u : 0u);
+          }
           ptx::umma_commit(&kv_empty[Cfg::k_slot(step)]);
           ptx::umma_commit(ds_free);
         }
@@ -806,7 +845,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
       if (idx < 0 || idx >= total_items) break;
       const QItem it = decode_q_item(p, idx);
       if (!it.valid) continue;
-      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kTile);
+      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
       const QSpans spans = make_q_spans(it, bs);
       const int r = it.qa + row;
       const bool row_valid = r < it.n;
@@ -819,36 +858,43 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
       for (int s = 0; s < plan.steps() && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
-        const int cls = spans.classify(kh, kt);
+        constexpr int kKc = Cfg::kKeyCols;
+        const int cls = spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys);
         if (cls == kTileSkip) continue;
         int lo = 0, hi = 0;
         if (cls == kTileMasked) {
           if (it.qh == 1) { lo = 0; hi = blk1; }
           else if (kh == 1) { lo = 0; hi = blk0; }
           else { lo = blk0; hi = blk1; }
-          lo -= kt * kTile + wg * kCols;
-          hi -= kt * kTile + wg * kCols;
+          lo -= kt * Cfg::kKeys + wg * kKc;
+          hi -= kt * Cfg::kKeys + wg * kKc;
         }
         if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 91)) { alive = false; break; }
         ptx::tc_fence_after();
-        uint32_t sv[kCols], dpv[kCols];
-        ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * kCols, sv);
-        ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * kCols, dpv);
+        uint32_t sv[kKc], dpv[kKc];
+        if (kKc == 32) {
+          ptx::tmem_ld32(tmem + Cfg::kTmemS + lane_addr + wg * kKc, sv);
+          ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + wg * kKc, dpv);
+        } else {
+          ptx::tmem_ld16(tmem + Cfg::kTmemS + lane_addr + wg * kKc, sv);
+          ptx::tmem_ld16(tmem + Cfg::kTmemDP + lane_addr + wg * kKc, dpv);
+        }
         ptx::tmem_wait_ld();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(sdp_free);
-        uint32_t pk_ds[kCols / 2];
+        uint32_t pk_ds[kKc / 2];
         if (cls == kTileMasked) {
-          softmax_backward_cols<kCols, kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
-                                                                      p.softcap_pre, lo, hi, nullptr, pk_ds);
+          softmax_backward_cols<kKc, kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta,
+                                                                          p.scale_log2, p.softcap_pre, lo, hi, nullptr, pk_ds);
         } else {
-          softmax_backward_cols<kCols, kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta, p.scale_log2,
-                                                                       p.softcap_pre, 0, 0, nullptr, pk_ds);
+          softmax_backward_cols<kKc, kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta,
+                                                                           p.scale_log2, p.softcap_pre, 0, 0, nullptr, pk_ds);
         }
         if (!ptx::mbar_wait(ds_free, (cnt & 1) ^ 1, abort_flag, 92)) { alive = false; break; }
         ++cnt;
         ptx::tc_fence_after();
-        ptx::tmem_st16(tmem + Cfg::kTmemDS + lane_addr + wg * (kCols / 2), pk_ds);
+        if (kKc == 32) ptx::tmem_st16(tmem + Cfg::kTmemDS + lane_addr + wg * (kKc / 2), pk_ds);
+        else ptx::tmem_st8(tmem + Cfg::kTmemDS + lane_addr + wg * (kKc / 2), pk_ds);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(ds_full);
@@ -899,7 +945,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     static bool done[16] = {false};
     int rc = set_smem(kernel, Cfg::kSmemBytes, done);
     if (rc) return rc;
-    const int items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+    const int items = p.tiles_per_half * 2 * p.heads_k * p.batch * Cfg::kPasses;
     const int grid = items < sm_count ? items : sm_count;
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
@@ -946,8 +992,7 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   if (rc) return rc;
   if (info.cc_major != 10) return FDA_ERR_ARCH;
   const int d = pr.head_dim;
-  if (d > 128) return FDA_ERR_UNSUPPORTED;
-  const int d_round = d <= 64 ? 64 : 128;
+  const int d_round = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
   const bool varlen = pr.cu_seqlens != nullptr;
   const int64_t rows = varlen ? pr.total : pr.seqlen;
   const int tma_batch = varlen ? 1 : pr.batch;
@@ -966,6 +1011,12 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   if (rc) return rc;
   rc = encode_tile_map(&p.tm_do64, a.dout.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.dout.row_stride,
                        a.dout.head_stride, a.dout.batch_stride, 64, kSub);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_k64, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
+                       a.k.head_stride, a.k.batch_stride, 64, 64);
+  if (rc) return rc;
+  rc = encode_tile_map(&p.tm_v64, a.v.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.v.row_stride,
+                       a.v.head_stride, a.v.batch_stride, 64, 64);
   if (rc) return rc;
   rc = encode_tile_map(&p.tm_k, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
                        a.k.head_stride, a.k.batch_stride, 64, kTile);
@@ -1050,7 +1101,8 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
     FDA_CUDA_TRY(cudaGetLastError());
   }
   if (d_round == 64) return dispatch_bwd<64, 6, 7>(p, sm_count, bf16, softcap, stage_mask, stream);
-  return dispatch_bwd<128, 4, 5>(p, sm_count, bf16, softcap, stage_mask, stream);
+  if (d_round == 128) return dispatch_bwd<128, 4, 5>(p, sm_count, bf16, softcap, stage_mask, stream);
+  return dispatch_bwd<256, 1, 3>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
 #ifdef FDA_WAIT_CLOCKS

@@ -130,3 +130,27 @@ def test_backward_matches_golden_fixture():
         truth = torch.from_numpy(gold[f"{name}/{key}"]).to(DEV)
         # the golden gradients were taken through a bf16-rounded forward output; allow that rounding too
         assert_within_2x(key, got, truth, pl, atol=3e-2)
+
+
+@pytest.mark.parametrize("heads,heads_k", [(4, 4), (4, 2)])
+@pytest.mark.parametrize("batch,n,bs", [(1, 256, 32), (2, 333, 16), (1, 517, 7), (1, 300, 128), (1, 640, 256), (2, 5, 2)])
+def test_backward_head_dim_256(batch, n, bs, heads, heads_k):
+    """Head dimension 256: the dK/dV kernel makes two passes over the d halves, the dQ kernel uses 64-key tiles."""
+    torch.manual_seed(n * 7 + bs)
+    q = torch.randn(batch, 2 * n, heads, 256, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, 256, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, 256, device=DEV, dtype=torch.bfloat16)
+    check_backward(q, k, v, bs)
+
+
+@pytest.mark.parametrize("d", [80, 96, 112, 160, 192, 224])
+@pytest.mark.parametrize("bs", [1, 4, 37])
+def test_backward_padded_head_dims(bs, d):
+    """Head dimensions between the kernel sizes are padded inside the kernels (zero-filled TMA columns); the
+    reference tests the same dims (tests/test_diffusion_attn.py:124-134 there)."""
+    torch.manual_seed(d)
+    batch, n, heads, heads_k = 2, 211, 4, 2
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    check_backward(q, k, v, bs)

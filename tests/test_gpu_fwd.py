@@ -120,3 +120,24 @@ def test_forward_matches_golden_fixture():
     plain = torch.from_numpy(gold[f"{name}/out_pt"]).to(DEV)
     assert_within_2x("out", out, truth, plain)
     assert (lse.cpu() - torch.from_numpy(gold[f"{name}/lse"])).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("heads,heads_k", [(4, 4), (4, 2)])
+@pytest.mark.parametrize("batch,n,bs", [(1, 256, 32), (2, 333, 16), (1, 517, 7), (1, 300, 128), (1, 640, 256), (2, 5, 2)])
+def test_forward_head_dim_256(batch, n, bs, heads, heads_k):
+    torch.manual_seed(n * 7 + bs)
+    q = torch.randn(batch, 2 * n, heads, 256, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, 256, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, 256, device=DEV, dtype=torch.bfloat16)
+    check_forward(q, k, v, bs)
+
+
+@pytest.mark.parametrize("d", [80, 96, 112, 160, 192, 224])
+@pytest.mark.parametrize("bs", [1, 4, 37])
+def test_forward_padded_head_dims(bs, d):
+    torch.manual_seed(d)
+    batch, n, heads, heads_k = 2, 211, 4, 2
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    check_forward(q, k, v, bs)
