@@ -56,6 +56,10 @@ struct FwdParams {
   int total_items;
   int* ticket;         // global work counter, zeroed before the launch
   int wide_store;      // rows of out allow 32-byte stores
+  const float* q_descale;  // FP8 only: (batch, heads_k) factors, element strides below; nullptr = 1
+  const float* k_descale;
+  const float* v_descale;
+  int64_t descale_bs[3], descale_hs[3];
   float scale_log2;    // exponent scale: softmax_scale*log2(e), or softcap*log2(e) with softcapping
   float softcap_pre;   // softmax_scale / softcap (tanh argument scale)
   float lse_scale;     // natural-log scale of the row maximum: softmax_scale, or softcap
@@ -121,11 +125,18 @@ __device__ __forceinline__ TileSpans make_tile_spans(const Item& it, int t, int 
   return ts;
 }
 
-template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
 struct FwdConfig {
-  static constexpr int kTileBytes = kBlockN * kHeadDim * 2;  // one 128-row tile of Q, K or V
-  static constexpr int kPanels = kHeadDim / 64;              // 64-column panels (128-byte rows)
+  // kType: 0 bf16, 1 fp16, 2 fp8 e4m3 (forward only; the output is bf16)
+  static constexpr bool kFp8 = kType == 2;
+  static constexpr int kElemBytes = kFp8 ? 1 : 2;
+  static constexpr int kTileBytes = kBlockN * kHeadDim * kElemBytes;  // one 128-row tile of Q, K or V
+  static constexpr int kPanelElems = 128 / kElemBytes;                // elements per 128-byte panel row
+  static constexpr int kPanels = kHeadDim / kPanelElems;
   static constexpr int kPanelBytes = 128 * 128;
+  static constexpr int kStepElems = 32 / kElemBytes;                  // reduction elements per MMA (32 bytes)
+  static constexpr int kPCols = kBlockN * kElemBytes / 4;             // tensor-memory columns of the packed P
+  static_assert(kHeadDim % kPanelElems == 0, "head dimension must fill whole 128-byte panels");
   static constexpr int kThreads = 128 * kQTiles + 64;
   static constexpr int kLoadWarp = 4 * kQTiles;
   static constexpr int kMmaWarp = 4 * kQTiles + 1;
@@ -135,9 +146,9 @@ struct FwdConfig {
   static_assert(kTmemO + kQTiles * kHeadDim <= 512, "tensor memory budget");
 };
 
-template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
 __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
-  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
+  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -216,7 +227,8 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
             const CUtensorMap* tm = which == 0 ? &p.tm_k : &p.tm_v;
 #pragma unroll
             for (int c = 0; c < Cfg::kPanels; ++c) {
-              ptx::tma_load_4d(dst + c * Cfg::kPanelBytes, tm, &kv_full[stage], c * 64, k_row, it.hk, it.bcoord);
+              ptx::tma_load_4d(dst + c * Cfg::kPanelBytes, tm, &kv_full[stage], c * Cfg::kPanelElems, k_row, it.hk,
+                               it.bcoord);
             }
             ++slot;
             if (s == 0 && which == 0) {
@@ -226,7 +238,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
               for (int t = 0; t < ntiles; ++t) {
 #pragma unroll
                 for (int c = 0; c < Cfg::kPanels; ++c) {
-                  ptx::tma_load_4d(sQ + t * Cfg::kTileBytes + c * Cfg::kPanelBytes, &p.tm_q, q_full, c * 64,
+                  ptx::tma_load_4d(sQ + t * Cfg::kTileBytes + c * Cfg::kPanelBytes, &p.tm_q, q_full, c * Cfg::kPanelElems,
                                    q_row + t * kBlockM, it.h, it.bcoord);
                 }
               }
@@ -240,7 +252,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
   } else if (warp == Cfg::kMmaWarp) {
     // --------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr int kFmt = kBf16 ? 1 : 0;
+      constexpr int kFmt = kType == 0 ? 1 : 0;  // kind::f16: 1 = bf16, 0 = f16; kind::f8f6f4: 0 = e4m3
       const uint32_t idesc_s = ptx::make_idesc(kBlockM, kBlockN, kFmt, false, false);
       const uint32_t idesc_o = ptx::make_idesc(kBlockM, kHeadDim, kFmt, false, true);
       uint32_t slot = 0, n_item = 0;
@@ -258,17 +270,21 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         const uint32_t a_lo = q_lo0 + t * (Cfg::kTileBytes >> 4);
         const uint32_t b_lo = k_lo0 + k_stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+        for (int kk = 0; kk < kHeadDim / Cfg::kStepElems; ++kk) {
           const uint32_t off = ((kk / 4) * Cfg::kPanelBytes + (kk % 4) * 32) >> 4;
-          ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS + t * 128, a_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
+          if (Cfg::kFp8) ptx::umma_ss_f8_lh(tmem + Cfg::kTmemS + t * 128, a_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
+          else ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS + t * 128, a_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
         }
       };
       auto issue_pv = [&](int t, uint32_t v_stage, bool accumulate) {
         const uint32_t b_lo = v_lo0 + v_stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemO + t * kHeadDim, tmem + Cfg::kTmemS + t * 128 + kk * 8,
-                              b_lo + kk * (2048 >> 4), kDescHi, idesc_o, (accumulate || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kBlockN / Cfg::kStepElems; ++kk) {
+          // one MMA consumes 32 bytes of every P row (8 columns) and kStepElems rows of V (128 bytes each)
+          const uint32_t a_t = tmem + Cfg::kTmemS + t * 128 + kk * 8;
+          const uint32_t b = b_lo + kk * ((Cfg::kStepElems * 128) >> 4);
+          if (Cfg::kFp8) ptx::umma_ts_f8_lh(tmem + Cfg::kTmemO + t * kHeadDim, a_t, b, kDescHi, idesc_o, (accumulate || kk > 0) ? 1u : 0u);
+          else ptx::umma_ts_f16_lh(tmem + Cfg::kTmemO + t * kHeadDim, a_t, b, kDescHi, idesc_o, (accumulate || kk > 0) ? 1u : 0u);
         }
       };
 
@@ -362,6 +378,26 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       const int r_eff = row_valid ? r : it.n - 1;
       const int blk0 = block_lo(r_eff, bs);
       const int blk1 = imin(blk0 + bs, it.n);
+      // FP8: the per-(sample, KV head) descales of q and k fold into the score scale, the descale of v into the
+      // final normalisation (the reference does the same, flash_fwd_kernel_sm90.h:299-305, mainloop_fwd...:818-822)
+      float scale_log2 = p.scale_log2, softcap_pre = p.softcap_pre, lse_scale = p.lse_scale, out_scale = 1.f;
+      if (Cfg::kFp8) {
+        float qk = 1.f;
+        if (p.q_descale != nullptr) qk *= p.q_descale[it.b * p.descale_bs[0] + it.hk * p.descale_hs[0]];
+        if (p.k_descale != nullptr) qk *= p.k_descale[it.b * p.descale_bs[1] + it.hk * p.descale_hs[1]];
+        if (p.v_descale != nullptr) out_scale = p.v_descale[it.b * p.descale_bs[2] + it.hk * p.descale_hs[2]];
+        if (kSoftcap) {
+          softcap_pre *= qk;
+        } else {
+          scale_log2 *= qk;
+          lse_scale *= qk;
+        }
+      }
+      // P is rounded to e4m3 for FP8: keep it in (0, 2^8] by advancing the maximum at every increase and shifting
+      // the exponent by 8 (the reference's Max_offset = 8, softmax.h:67-69 there); 16-bit P may run up to 2^8
+      // above 1 before the maximum is advanced.
+      constexpr float kThreshold = Cfg::kFp8 ? 0.f : kRescaleThreshold;
+      constexpr float kPShift = Cfg::kFp8 ? 8.f : 0.f;
       float m_run = -INFINITY;  // reference maximum (unscaled scores, or tanh values with softcap)
       float l_run = 0.f;
       bool o_started = false;
@@ -398,7 +434,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         }
         if (kSoftcap) {
 #pragma unroll
-          for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * p.softcap_pre);
+          for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * softcap_pre);
         }
         if (cls == kTileMasked) {
           int lo, hi;
@@ -426,9 +462,9 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
                                    fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         const float m_new = fmaxf(m_run, m_tile);
         // advance the reference maximum only when it grew by more than the threshold (always on the first tile)
-        const bool need = (m_new - m_run) * p.scale_log2 > kRescaleThreshold;
+        const bool need = (m_new - m_run) * scale_log2 > kThreshold;
         if (__any_sync(0xffffffffu, need)) {
-          const float factor = need ? ptx::ex2((m_run - m_new) * p.scale_log2) : 1.f;
+          const float factor = need ? ptx::ex2((m_run - m_new) * scale_log2) : 1.f;
           if (o_started) {
 #pragma unroll
             for (int c = 0; c < kHeadDim / 32; ++c) {
@@ -444,15 +480,27 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
           if (need) m_run = m_new;
         }
         const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
-        const float neg_m = -m_ref * p.scale_log2;
+        const float neg_m = kPShift - m_ref * scale_log2;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[kBlockN / 2];
+        uint32_t pk[Cfg::kPCols];
+        if (Cfg::kFp8) {
 #pragma unroll
-        for (int c = 0; c < kBlockN; c += 2) {
-          const float p0 = ptx::ex2(fmaf(v[c], p.scale_log2, neg_m));
-          const float p1 = ptx::ex2(fmaf(v[c + 1], p.scale_log2, neg_m));
-          sum4[(c / 2) & 3] += p0 + p1;
-          pk[c / 2] = ptx::pack2<kBf16>(p0, p1);
+          for (int c = 0; c < kBlockN; c += 4) {
+            const float p0 = ptx::ex2(fmaf(v[c], scale_log2, neg_m));
+            const float p1 = ptx::ex2(fmaf(v[c + 1], scale_log2, neg_m));
+            const float p2 = ptx::ex2(fmaf(v[c + 2], scale_log2, neg_m));
+            const float p3 = ptx::ex2(fmaf(v[c + 3], scale_log2, neg_m));
+            sum4[(c / 4) & 3] += (p0 + p1) + (p2 + p3);
+            pk[c / 4] = ptx::pack_e4m3x4(p0, p1, p2, p3);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < kBlockN; c += 2) {
+            const float p0 = ptx::ex2(fmaf(v[c], scale_log2, neg_m));
+            const float p1 = ptx::ex2(fmaf(v[c + 1], scale_log2, neg_m));
+            sum4[(c / 2) & 3] += p0 + p1;
+            pk[c / 2] = ptx::pack2<kType == 0>(p0, p1);
+          }
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         if (kQTiles > 1 && kUseMufuLock) {
@@ -461,7 +509,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         }
         FDA_PH(ph_math);
 #pragma unroll
-        for (int c = 0; c < kBlockN / 64; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
+        for (int c = 0; c < Cfg::kPCols / 32; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&p_full[t]);
@@ -478,7 +526,7 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
       FDA_PH(ph_owait);
       ++cnt_o;
       ptx::tc_fence_after();
-      const float inv_l = 1.f / l_run;
+      const float inv_l = out_scale / l_run;
       const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
       {
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + it.bcoord * p.o_batch_stride + srow * p.o_row_stride +
@@ -495,14 +543,14 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
           if (row_valid) {
 #pragma unroll
             for (int c = 0; c < kPassCols / 32; ++c) {
-              ptx::store_row32<kBf16>(orow, pass * 128 + c * 32, o + c * 32, inv_l, p.head_dim, p.wide_store != 0);
+              ptx::store_row32<kType != 1>(orow, pass * 128 + c * 32, o + c * 32, inv_l, p.head_dim, p.wide_store != 0);
             }
           }
         }
       }
       if (row_valid) {
         const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
-        const float lse = (l_run > 0.f) ? m_ref * p.lse_scale + __log2f(l_run) * kLn2 : -INFINITY;
+        const float lse = (l_run > 0.f) ? m_ref * lse_scale + (__log2f(l_run) - kPShift) * kLn2 : -INFINITY;
         const int64_t li = (p.cu_seqlens != nullptr)
                                ? static_cast<int64_t>(it.h) * p.total + srow
                                : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
@@ -533,10 +581,10 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
 }
 #undef FDA_PH
 
-template <int kHeadDim, int kQTiles, int kStages, bool kBf16, bool kSoftcap>
+template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
 int launch_fwd_instance(const FwdParams& p, int grid, cudaStream_t stream) {
-  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
-  auto kernel = fwd_kernel<kHeadDim, kQTiles, kStages, kBf16, kSoftcap>;
+  using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
+  auto kernel = fwd_kernel<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
   static bool attr_set[16] = {false};
   int dev = 0;
   FDA_CUDA_TRY(cudaGetDevice(&dev));
@@ -552,26 +600,35 @@ int launch_fwd_instance(const FwdParams& p, int grid, cudaStream_t stream) {
 template <int kHeadDim, int kQTiles, int kStages>
 int dispatch_fwd(const FwdParams& p, int grid, bool bf16, bool softcap, cudaStream_t stream) {
   if (bf16) {
-    return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, true, true>(p, grid, stream)
-                   : launch_fwd_instance<kHeadDim, kQTiles, kStages, true, false>(p, grid, stream);
+    return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, 0, true>(p, grid, stream)
+                   : launch_fwd_instance<kHeadDim, kQTiles, kStages, 0, false>(p, grid, stream);
   }
-  return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, false, true>(p, grid, stream)
-                 : launch_fwd_instance<kHeadDim, kQTiles, kStages, false, false>(p, grid, stream);
+  return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, 1, true>(p, grid, stream)
+                 : launch_fwd_instance<kHeadDim, kQTiles, kStages, 1, false>(p, grid, stream);
+}
+
+template <int kHeadDim, int kQTiles, int kStages>
+int dispatch_fwd_fp8(const FwdParams& p, int grid, bool softcap, cudaStream_t stream) {
+  return softcap ? launch_fwd_instance<kHeadDim, kQTiles, kStages, 2, true>(p, grid, stream)
+                 : launch_fwd_instance<kHeadDim, kQTiles, kStages, 2, false>(p, grid, stream);
 }
 
 }  // namespace
 
 int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   const FdaProblem& pr = a.p;
-  if (pr.dtype == FDA_E4M3) return FDA_ERR_UNSUPPORTED;
   DeviceInfo info;
   int rc = current_device_info(&info);
   if (rc) return rc;
   if (info.cc_major != 10) return FDA_ERR_ARCH;
 
   const int d = pr.head_dim;
-  const int d_round = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
+  const bool fp8 = pr.dtype == FDA_E4M3;
+  // FP8 rows are padded to whole 128-byte panels, so the smallest FP8 kernel is the 128-wide one
+  const int d_round = (d <= 64 && !fp8) ? 64 : (d <= 128 ? 128 : 256);
   const int q_tiles = d_round <= 128 ? 2 : 1;
+  const int eb = fp8 ? 1 : 2;
+  const int box_cols = 128 / eb;
   const bool varlen = pr.cu_seqlens != nullptr;
   const int64_t rows = varlen ? pr.total : pr.seqlen;
   const int tma_batch = varlen ? 1 : pr.batch;
@@ -579,15 +636,24 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
 
   FwdParams p;
   memset(&p, 0, sizeof(p));
-  rc = encode_tile_map(&p.tm_q, a.q.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.q.row_stride,
-                       a.q.head_stride, a.q.batch_stride, 64, kBlockM);
+  rc = encode_tile_map(&p.tm_q, a.q.ptr, eb, fp8, fp16, d, rows, pr.heads, tma_batch, a.q.row_stride,
+                       a.q.head_stride, a.q.batch_stride, box_cols, kBlockM);
   if (rc) return rc;
-  rc = encode_tile_map(&p.tm_k, a.k.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
-                       a.k.head_stride, a.k.batch_stride, 64, kBlockN);
+  rc = encode_tile_map(&p.tm_k, a.k.ptr, eb, fp8, fp16, d, rows, pr.heads_k, tma_batch, a.k.row_stride,
+                       a.k.head_stride, a.k.batch_stride, box_cols, kBlockN);
   if (rc) return rc;
-  rc = encode_tile_map(&p.tm_v, a.v.ptr, 2, false, fp16, d, rows, pr.heads_k, tma_batch, a.v.row_stride,
-                       a.v.head_stride, a.v.batch_stride, 64, kBlockN);
+  rc = encode_tile_map(&p.tm_v, a.v.ptr, eb, fp8, fp16, d, rows, pr.heads_k, tma_batch, a.v.row_stride,
+                       a.v.head_stride, a.v.batch_stride, box_cols, kBlockN);
   if (rc) return rc;
+  if (fp8) {
+    p.q_descale = a.q_descale;
+    p.k_descale = a.k_descale;
+    p.v_descale = a.v_descale;
+    for (int i = 0; i < 3; ++i) {
+      p.descale_bs[i] = a.descale_batch_stride[i];
+      p.descale_hs[i] = a.descale_head_stride[i];
+    }
+  }
   p.out = a.out.ptr;
   p.lse = a.lse;
   p.o_batch_stride = varlen ? 0 : a.out.batch_stride;
@@ -626,6 +692,10 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   if (grid < 1) grid = 1;
   if (grid > p.total_items) grid = p.total_items;
   const bool bf16 = pr.dtype == FDA_BF16;
+  if (fp8) {
+    if (d_round == 128) return dispatch_fwd_fp8<128, 2, 6>(p, grid, softcap, stream);
+    return dispatch_fwd_fp8<256, 1, 4>(p, grid, softcap, stream);
+  }
   if (d_round == 64) return dispatch_fwd<64, 2, 6>(p, grid, bf16, softcap, stream);
   if (d_round == 128) return dispatch_fwd<128, 2, 4>(p, grid, bf16, softcap, stream);
   return dispatch_fwd<256, 1, 2>(p, grid, bf16, softcap, stream);
