@@ -133,6 +133,20 @@ class ClockSampler:
                     samples=len(self.mhz), source="nvml" if self._nvml is not None else "nvidia-smi")
 
 
+def shard_seed(rank):
+    """Every rank owns its own B=8 shard of the global batch: independent samples from its own seed."""
+    return 1234 + rank
+
+
+def max_over_ranks(value, dist_module, world, device):
+    """Largest `value` (float) over all ranks; identity when there is one rank."""
+    if world <= 1:
+        return float(value)
+    t = torch.tensor([float(value)], device=device, dtype=torch.float64)
+    dist_module.all_reduce(t, op=dist_module.ReduceOp.MAX)
+    return float(t.item())
+
+
 def make_cpu_sample(threads=None):
     """The bounded CPU sample of the workload: ONE sample x 2 heads of the C2 shape (same n, head_dim,
     block_size), float32 forward + explicit backward with the oracle. Returns (run_once, flops, description)."""
@@ -228,7 +242,7 @@ def main():
 
     w = WORKLOAD
     B, n, H, Hk, d, bs = w["batch"], w["n"], w["heads"], w["heads_k"], w["head_dim"], w["block_size"]
-    gen = torch.Generator().manual_seed(1234 + rank)
+    gen = torch.Generator().manual_seed(shard_seed(rank))
     host = [torch.randn(B, 2 * n, h, d, generator=gen).to(torch.bfloat16).pin_memory() for h in (H, Hk, Hk, H)]
     q, k, v, do = (t.to(dev) for t in host)
     fwd_flops, bwd_flops = orc.step_flops([n] * B, bs, H, d)
@@ -275,10 +289,7 @@ def main():
         e_end.record()
         barrier()
     total_ms = e_start.elapsed_time(e_end)
-    ms_t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-    ms_per_step = ms_t.item() / args.steps
+    ms_per_step = max_over_ranks(total_ms, dist, world, dev) / args.steps
     value = step_flops * world / (ms_per_step * 1e-3) / 1e12
 
     names = ["fwd_kernel", "bwd_preprocess_kernel", "bwd_dkdv_kernel", "bwd_dq_kernel"]
@@ -322,10 +333,7 @@ def main():
             step_e2e()
         e_end.record()
         barrier()
-        t = torch.tensor([e_start.elapsed_time(e_end)], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item() / e2e_steps
+        e2e_ms = max_over_ranks(e_start.elapsed_time(e_end), dist, world, dev) / e2e_steps
         e2e = dict(value=step_flops * world / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS",
                    h2d_bytes_per_step=sum(t.numel() * 2 for t in host),
                    d2h_bytes_per_step=sum(t.numel() * 2 for t in outs_host), ms_per_step=e2e_ms)
