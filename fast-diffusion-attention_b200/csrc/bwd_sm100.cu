@@ -291,7 +291,8 @@ struct DkdvCfg {
   using T = TileCfg<kHeadDim>;
   static constexpr int kSubTileBytes = kSub * kHeadDim * 2;     // Q or dO sub-tile
   static constexpr int kSubPanelBytes = kSub * 128;             // one 64-column panel of a sub-tile
-  static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64]
+  static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64], header
+  static constexpr int kHeaderOffset = 2 * kSubTileBytes + 512;
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
   static constexpr int kThreads = kBwdThreads;
   // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
@@ -403,10 +404,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         const int k_row = it.row0 + it.kh * it.n + it.k0;
         load_tile<kHeadDim>(sK, &p.tm_k, kv_full, k_row, it.hk, it.bcoord);
         load_tile<kHeadDim>(sV, &p.tm_v, kv_full, k_row, it.hk, it.bcoord);
-        alive = for_each_substep(it, plan, spans, [&](const SubStep& st) -> bool {
+        // The loader alone walks the item's geometry. Each stage carries a two-word header for the other roles:
+        // {bit 0 last sub-step of the item, bit 1 partially masked, bit 2 queries of the keys' own half; first row}.
+        // A sub-step is sent when its successor is known, so that the last one can be marked.
+        auto emit = [&](const SubStep& st, bool last) -> bool {
           const uint32_t stage = gc % kStages;
           if (!ptx::mbar_wait(&st_empty[stage], ((gc / kStages) & 1) ^ 1, abort_flag, 42)) return false;
           uint8_t* base = sStage + stage * Cfg::kStageBytes;
+          volatile int* hdr = reinterpret_cast<volatile int*>(base + Cfg::kHeaderOffset);
+          hdr[0] = (last ? 1 : 0) | (st.cls == kTileMasked ? 2 : 0) | (st.qh == it.kh ? 4 : 0);
+          hdr[1] = st.sa;
           ptx::mbar_expect_tx(&st_full[stage], 2 * Cfg::kSubTileBytes + 512);
           const int q_row = it.row0 + st.qh * it.n + st.sa;
 #pragma unroll
@@ -420,7 +427,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes + 256, p.delta_pad + seg, 256, &st_full[stage]);
           ++gc;
           return true;
+        };
+        SubStep pend{};
+        bool have = false;
+        alive = for_each_substep(it, plan, spans, [&](const SubStep& st) -> bool {
+          if (have && !emit(pend, false)) return false;
+          pend = st;
+          have = true;
+          return true;
         });
+        // every valid key tile is seen at least by the queries of its own rows, so there is a last sub-step
+        if (alive && have) alive = emit(pend, true);
         ++n_item;
       }
       if (*abort_flag) __nanosleep(100000);
@@ -472,17 +489,16 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         if (idx < 0 || idx >= total_items) break;
         const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
         if (!it.valid) continue;
-        const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
-        const KvSpans spans = make_kv_spans(it, bs);
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
         acc = false;
         pass_panel_off = (idx % Cfg::kPasses) * (Cfg::kAccDim / 64) * (Cfg::kSubPanelBytes >> 4);
-        alive = for_each_substep(it, plan, spans, [&](const SubStep&) -> bool {
+        for (bool last = false; alive && !last;) {
           if (g_issued - g_done == Cfg::kLookahead) {
-            if (!retire()) return false;
+            if (!retire()) { alive = false; break; }
           }
           const uint32_t u = g_issued & 1u, stage = g_issued % kStages;
-          if (!ptx::mbar_wait(&st_full[stage], (g_issued / kStages) & 1u, abort_flag, 52)) return false;
+          if (!ptx::mbar_wait(&st_full[stage], (g_issued / kStages) & 1u, abort_flag, 52)) { alive = false; break; }
+          last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
           ptx::tc_fence_after();
           const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
           const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
@@ -500,8 +516,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           }
           ptx::umma_commit(&sdp_full[u]);
           ++g_issued;
-          return true;
-        });
+        }
         while (alive && g_done < g_issued) alive = retire();
         if (!alive) break;
         ptx::umma_commit(kv_empty);
@@ -523,19 +538,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
       const int pass_col0 = (idx % Cfg::kPasses) * Cfg::kAccDim;
       if (!it.valid) continue;
-      const QueryPlan plan = make_query_plan(it.kh, it.k0, it.k1, it.n, bs, kTile);
-      const KvSpans spans = make_kv_spans(it, bs);
       const int kj = it.k0 + row;
       // queries that see this thread's key: same-half tiles and (clean keys only) noisy tiles of later blocks
       int same_lo, same_hi, cross_lo, cross_hi;
       query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
       query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
-      alive = for_each_substep(it, plan, spans, [&](const SubStep& st) -> bool {
+      for (bool last = false; alive && !last;) {
         const uint32_t u = gc & 1u, stage = gc % kStages;
-        const float* stats = reinterpret_cast<const float*>(sStage + stage * Cfg::kStageBytes + 2 * Cfg::kSubTileBytes);
-        // wait on the stage barrier ourselves: it orders the bulk copies of lse2 / delta before our reads
-        if (!ptx::mbar_wait(&st_full[stage], (gc / kStages) & 1u, abort_flag, 60)) return false;
-        if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) return false;
+        const uint8_t* stage_base = sStage + stage * Cfg::kStageBytes;
+        const float* stats = reinterpret_cast<const float*>(stage_base + 2 * Cfg::kSubTileBytes);
+        // wait on the stage barrier ourselves: it orders the header and the bulk copies of lse2 / delta before our reads
+        if (!ptx::mbar_wait(&st_full[stage], (gc / kStages) & 1u, abort_flag, 60)) { alive = false; break; }
+        int2 hdr;
+        hdr.x = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[0];
+        hdr.y = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[1];
+        last = (hdr.x & 1) != 0;
+        if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) { alive = false; break; }
         ++gc;
         ptx::tc_fence_after();
         const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
@@ -547,9 +565,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
         const float* l2 = stats + wg * kSubCols;
         const float* dl = stats + kSub + wg * kSubCols;
-        if (st.cls == kTileMasked) {
-          const int lo = (st.qh == it.kh ? same_lo : cross_lo) - (st.sa + wg * kSubCols);
-          const int hi = (st.qh == it.kh ? same_hi : cross_hi) - (st.sa + wg * kSubCols);
+        if (hdr.x & 2) {
+          const int lo = ((hdr.x & 4) ? same_lo : cross_lo) - (hdr.y + wg * kSubCols);
+          const int hi = ((hdr.x & 4) ? same_hi : cross_hi) - (hdr.y + wg * kSubCols);
           softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, true, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
                                                                               p.softcap_pre, lo, hi, pk_p, pk_ds);
         } else {
@@ -563,8 +581,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&pds_full[u]);
-        return true;
-      });
+      }
       if (!alive) break;
       if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
       ++n_item;
