@@ -27,6 +27,26 @@
 #include "ptx.cuh"
 #include "sched.cuh"
 
+#ifndef FDA_ABL
+#define FDA_ABL 0   // debug builds only: 1 skips the softmax-backward arithmetic, 2 also the tensor-memory traffic
+#endif
+
+#ifdef FDA_TRACE
+__device__ long long g_fda_trace[8 * 256];
+extern "C" int fda_debug_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fda_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : 1;
+}
+#define FDA_TRACE_AT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define FDA_TRACE_AT(row, idx) do { } while (0)
+#endif
+#ifdef FDA_CLOCKRATE
+__device__ unsigned long long g_fda_clockrate[2];
+extern "C" int fda_debug_clockrate(unsigned long long* out2) {
+  return cudaMemcpyFromSymbol(out2, g_fda_clockrate, 16) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 namespace fda {
 namespace {
 
@@ -294,7 +314,7 @@ struct DkdvCfg {
   static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64], header
   static constexpr int kHeaderOffset = 2 * kSubTileBytes + 512;
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
-  static constexpr int kThreads = kBwdThreads;
+  static constexpr int kThreads = kBwdThreads + 32;  // a second MMA-issuing warp
   // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
   // head dimensions above 128 do not leave room for both accumulators next to the S^T / dP^T buffers: the key
   // tile is then processed in kPasses passes, each producing kAccDim columns of dK and dV
@@ -313,7 +333,7 @@ struct SubStep {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DkdvCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -329,14 +349,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   uint64_t* sdp_full = st_empty + kStages;   // [2]
   uint64_t* pds_full = sdp_full + 2;         // [2]
   uint64_t* acc_full = pds_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* buf_free = acc_full + 1;         // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FDA_CLOCKRATE
+  long long cr_c0 = 0; unsigned long long cr_t0 = 0;
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    cr_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cr_t0));
+  }
+#endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 4 * kCmpWG + 1);
+    sched_init(mbox, 4 * kCmpWG + 2);
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -346,6 +374,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     for (int u = 0; u < 2; ++u) {
       ptx::mbar_init(&sdp_full[u], 1);
       ptx::mbar_init(&pds_full[u], 4 * kCmpWG);
+      ptx::mbar_init(&buf_free[u], 1);
     }
     ptx::mbar_init(acc_full, 1);
     ptx::fence_mbar_init();
@@ -414,14 +443,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           volatile int* hdr = reinterpret_cast<volatile int*>(base + Cfg::kHeaderOffset);
           hdr[0] = (last ? 1 : 0) | (st.cls == kTileMasked ? 2 : 0) | (st.qh == it.kh ? 4 : 0);
           hdr[1] = st.sa;
+#if FDA_ABL >= 3
+          ptx::mbar_expect_tx(&st_full[stage], 512);
+#else
           ptx::mbar_expect_tx(&st_full[stage], 2 * Cfg::kSubTileBytes + 512);
+#endif
           const int q_row = it.row0 + st.qh * it.n + st.sa;
+#if FDA_ABL < 3
 #pragma unroll
           for (int c = 0; c < T::kPanels; ++c) {
             ptx::tma_load_4d(base + c * Cfg::kSubPanelBytes, &p.tm_q64, &st_full[stage], c * 64, q_row, st.h, it.bcoord);
             ptx::tma_load_4d(base + Cfg::kSubTileBytes + c * Cfg::kSubPanelBytes, &p.tm_do64, &st_full[stage], c * 64,
                              q_row, st.h, it.bcoord);
           }
+#endif
           const int64_t seg = stat_segment(p, it.b, st.h, st.qh) + st.sa;
           ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes, p.lse2_pad + seg, 256, &st_full[stage]);
           ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes + 256, p.delta_pad + seg, 256, &st_full[stage]);
@@ -443,62 +478,32 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       if (*abort_flag) __nanosleep(100000);
     }
   } else if (warp == kMmaWarpB) {
-    // ---------------------------------------------------------------------------------------------- MMA issuer
+    // ------------------------------------------------------------------- MMA issuer 1: S^T = K Q^T, dP^T = V dO^T
+    // Two threads issue the MMAs of this kernel. The tensor pipe's queue is short, so whatever else an issuing
+    // thread does (barrier waits, commits) leaves the pipe idle; with two issuers one's bookkeeping overlaps the
+    // other's MMAs. Their only mutual dependency is the S^T / dP^T buffer: sub-step g may overwrite buffer g & 1
+    // once dV / dK of sub-step g - 2 have read it (buf_free).
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, kSub, kFmt, false, false);
-      const uint32_t idesc_g = ptx::make_idesc(kTile, Cfg::kAccDim, kFmt, false, true);
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
-      uint32_t pass_panel_off = 0;  // descriptor offset of the first 64-column panel of this pass in a sub-tile
       const uint32_t k_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t v_lo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
-      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);                      // K-major use
-      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), Cfg::kSubPanelBytes);    // MN-major use
-      uint32_t n_item = 0, g_issued = 0, g_done = 0;
+      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);
+      uint32_t n_item = 0, g = 0;
       bool alive = true;
-      bool acc = false;
-
-      // dV += P^T dO and dK += dS^T Q of the oldest sub-step whose S^T / dP^T are outstanding
-      auto retire = [&]() -> bool {
-        const uint32_t u = g_done & 1u, stage = g_done % kStages;
-        if (!ptx::mbar_wait(&pds_full[u], (g_done >> 1) & 1u, abort_flag, 53)) return false;
-        ptx::tc_fence_after();
-        const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
-        const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
-        const uint32_t st_t = tmem + u * 128, dpt_t = tmem + u * 128 + 64;
-#pragma unroll
-        for (int kk = 0; kk < kSub / 16; ++kk) {
-          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols,
-                              st_lo_mn + do_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
-                              (acc || kk > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < kSub / 16; ++kk) {
-          ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDK, dpt_t + kk * kSubCols,
-                              st_lo_mn + q_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
-                              (acc || kk > 0) ? 1u : 0u);
-        }
-        acc = true;
-        ptx::umma_commit(&st_empty[stage]);
-        ++g_done;
-        return true;
-      };
-
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
         if (idx < 0 || idx >= total_items) break;
         const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
         if (!it.valid) continue;
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
-        acc = false;
-        pass_panel_off = (idx % Cfg::kPasses) * (Cfg::kAccDim / 64) * (Cfg::kSubPanelBytes >> 4);
-        for (bool last = false; alive && !last;) {
-          if (g_issued - g_done == Cfg::kLookahead) {
-            if (!retire()) { alive = false; break; }
-          }
-          const uint32_t u = g_issued & 1u, stage = g_issued % kStages;
-          if (!ptx::mbar_wait(&st_full[stage], (g_issued / kStages) & 1u, abort_flag, 52)) { alive = false; break; }
+        for (bool last = false; alive && !last; ++g) {
+          const uint32_t u = g & 1u, stage = g % kStages;
+          if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 52)) { alive = false; break; }
           last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
+          if (!ptx::mbar_wait(&buf_free[u], ((g >> 1) & 1u) ^ 1u, abort_flag, 54)) { alive = false; break; }
+          FDA_TRACE_AT(3, g);
           ptx::tc_fence_after();
           const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
           const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
@@ -507,21 +512,61 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
             const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
             const uint32_t b_off = ((kk / 4) * Cfg::kSubPanelBytes + (kk % 4) * 32) >> 4;
             ptx::umma_ss_f16_lh(tmem + u * 128, k_lo + a_off, st_lo_k + q_off + b_off, kHi, idesc_s, kk > 0);
-          }
-#pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
-            const uint32_t b_off = ((kk / 4) * Cfg::kSubPanelBytes + (kk % 4) * 32) >> 4;
             ptx::umma_ss_f16_lh(tmem + u * 128 + 64, v_lo + a_off, st_lo_k + do_off + b_off, kHi, idesc_s, kk > 0);
           }
           ptx::umma_commit(&sdp_full[u]);
-          ++g_issued;
+          FDA_TRACE_AT(4, g);
         }
-        while (alive && g_done < g_issued) alive = retire();
+        ++n_item;
+      }
+    }
+  } else if (warp == kMmaWarpB + 1) {
+    // ------------------------------------------------------------------- MMA issuer 2: dV += P^T dO, dK += dS^T Q
+    if (lane == 0) {
+      constexpr int kFmt = kBf16 ? 1 : 0;
+      const uint32_t idesc_g = ptx::make_idesc(kTile, Cfg::kAccDim, kFmt, false, true);
+      constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
+      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), Cfg::kSubPanelBytes);    // MN-major use
+      uint32_t g = 0;
+      bool alive = true;
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
+        const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
+        if (!it.valid) continue;
+        // descriptor offset of the first 64-column panel of this pass in a sub-tile
+        const uint32_t pass_panel_off = (idx % Cfg::kPasses) * (Cfg::kAccDim / 64) * (Cfg::kSubPanelBytes >> 4);
+        bool acc = false;
+        for (bool last = false; alive && !last; ++g) {
+          const uint32_t u = g & 1u, stage = g % kStages;
+          // the stage barrier orders the header and, through the other issuer's wait on it, nothing else here:
+          // the tiles themselves are read by the MMAs, after P^T / dS^T (pds_full) which follow S^T / dP^T
+          if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 55)) { alive = false; break; }
+          last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
+          FDA_TRACE_AT(0, g);
+          if (!ptx::mbar_wait(&pds_full[u], (g >> 1) & 1u, abort_flag, 53)) { alive = false; break; }
+          FDA_TRACE_AT(1, g);
+          ptx::tc_fence_after();
+          const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
+          const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
+          const uint32_t st_t = tmem + u * 128, dpt_t = tmem + u * 128 + 64;
+#pragma unroll
+          for (int kk = 0; kk < kSub / 16; ++kk) {
+            ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols,
+                                st_lo_mn + do_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
+                                (acc || kk > 0) ? 1u : 0u);
+            ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDK, dpt_t + kk * kSubCols,
+                                st_lo_mn + q_off + pass_panel_off + kk * (2048 >> 4), kHi, idesc_g,
+                                (acc || kk > 0) ? 1u : 0u);
+          }
+          acc = true;
+          ptx::umma_commit(&buf_free[u]);
+          ptx::umma_commit(&st_empty[stage]);
+          FDA_TRACE_AT(2, g);
+        }
         if (!alive) break;
         ptx::umma_commit(kv_empty);
         ptx::umma_commit(acc_full);
-        ++n_item;
       }
     }
   } else {
@@ -553,34 +598,50 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         hdr.x = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[0];
         hdr.y = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[1];
         last = (hdr.x & 1) != 0;
+        if (threadIdx.x == 0) FDA_TRACE_AT(5, gc);
         if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) { alive = false; break; }
+        if (threadIdx.x == 0) FDA_TRACE_AT(6, gc);
         ++gc;
         ptx::tc_fence_after();
         const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
         const uint32_t dpt_t = st_t + 64;
         uint32_t sv[kSubCols], dpv[kSubCols];
+#if FDA_ABL < 2
         ptx::tmem_ld16(st_t, sv);
         ptx::tmem_ld16(dpt_t, dpv);
         ptx::tmem_wait_ld();
+#else
+        for (int i = 0; i < kSubCols; ++i) { sv[i] = i; dpv[i] = i; }
+#endif
         uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
         const float* l2 = stats + wg * kSubCols;
         const float* dl = stats + kSub + wg * kSubCols;
+#if FDA_ABL >= 1
+        for (int i = 0; i < kSubCols / 2; ++i) { pk_p[i] = sv[i]; pk_ds[i] = dpv[i]; }
+        if (false) {
+#else
         if (hdr.x & 2) {
+#endif
           const int lo = ((hdr.x & 4) ? same_lo : cross_lo) - (hdr.y + wg * kSubCols);
           const int hi = ((hdr.x & 4) ? same_hi : cross_hi) - (hdr.y + wg * kSubCols);
           softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, true, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
                                                                               p.softcap_pre, lo, hi, pk_p, pk_ds);
         } else {
+#if FDA_ABL < 1
           softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, false, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
                                                                                p.softcap_pre, 0, 0, pk_p, pk_ds);
+#endif
         }
         // a warp overwrites only columns it has itself already loaded: its packed P^T / dS^T pieces go to the
         // start of its own kSubCols columns
+#if FDA_ABL < 2
         ptx::tmem_st8(st_t, pk_p);
         ptx::tmem_st8(dpt_t, pk_ds);
         ptx::tmem_wait_st();
+#endif
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&pds_full[u]);
+        if (threadIdx.x == 0) FDA_TRACE_AT(7, gc - 1);
       }
       if (!alive) break;
       if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
@@ -615,6 +676,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   }
   ptx::tc_fence_before();
   __syncthreads();
+#ifdef FDA_CLOCKRATE
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    g_fda_clockrate[0] = clock64() - cr_c0;
+    g_fda_clockrate[1] = t1 - cr_t0;
+  }
+#endif
   if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
@@ -680,7 +749,7 @@ struct DqCfg {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DqCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -705,7 +774,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 4 * kCmpWG + 1);
+    sched_init(mbox, 4 * kCmpWG + 2);
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -773,16 +842,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
       if (*abort_flag) __nanosleep(100000);
     }
   } else if (warp == kMmaWarpB) {
+    // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T and dP = dO V^T
+    // As in the dK/dV kernel two threads issue MMAs, so that the barrier waits of one overlap the MMAs of the
+    // other. They share nothing but the compute warps between them: S / dP of step j + 1 may start as soon as the
+    // compute warps have S / dP of step j in registers, whatever the state of dQ.
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, Cfg::kKeys, kFmt, false, false);
-      const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
       const uint32_t q_lo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
       const uint32_t do_lo = ptx::smem_desc_lo(ptx::smem_u32(sdO), 16);
       const uint32_t kv_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sKV), 16);
-      const uint32_t kv_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV), Cfg::kKvPanelBytes);
-      uint32_t n_item = 0, slot = 0, cnt_sdp = 0, cnt_ds = 0;
+      uint32_t n_item = 0, step = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
@@ -798,13 +869,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           active += spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) != kTileSkip;
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
-        // S/dP of step j+1 are issued before dQ of step j so the tensor pipe has work during the softmax math
-        auto issue_sdp = [&](uint32_t step) -> bool {
+        ++n_item;
+        for (int j = 0; j < active; ++j, ++step) {
           const uint32_t ks = Cfg::k_slot(step), vs = Cfg::v_slot(step);
-          if (!ptx::mbar_wait(sdp_free, (cnt_sdp & 1) ^ 1, abort_flag, 82)) return false;
-          ++cnt_sdp;
-          if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) return false;
-          if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) return false;
+          if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) { alive = false; break; }
+          if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) { alive = false; break; }
+          if (!ptx::mbar_wait(sdp_free, (step & 1) ^ 1, abort_flag, 82)) { alive = false; break; }
           ptx::tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
@@ -812,42 +882,55 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
             const uint32_t b_off = ((kk / 4) * Cfg::kKvPanelBytes + (kk % 4) * 32) >> 4;
             ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS, q_lo + a_off, kv_lo_k + ks * (Cfg::kKvTileBytes >> 4) + b_off, kHi,
                                 idesc_s, kk > 0);
-          }
-#pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
-            const uint32_t b_off = ((kk / 4) * Cfg::kKvPanelBytes + (kk % 4) * 32) >> 4;
             ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDP, do_lo + a_off, kv_lo_k + vs * (Cfg::kKvTileBytes >> 4) + b_off, kHi,
                                 idesc_s, kk > 0);
           }
           ptx::umma_commit(sdp_full);
           ptx::umma_commit(&kv_empty[vs]);  // V tile no longer needed
-          return true;
-        };
-        if (!issue_sdp(slot)) break;
-        for (int j = 0; j < active && alive; ++j) {
-          const uint32_t step = slot + j;
-          if (j + 1 < active) {
-            if (!issue_sdp(step + 1)) { alive = false; break; }
-          }
-          if (!ptx::mbar_wait(ds_full, cnt_ds & 1, abort_flag, 85)) { alive = false; break; }
-          ++cnt_ds;
+        }
+      }
+    }
+  } else if (warp == kMmaWarpB + 1) {
+    // ------------------------------------------------------------------------------ MMA issuer 2: dQ += dS K
+    if (lane == 0) {
+      constexpr int kFmt = kBf16 ? 1 : 0;
+      const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);
+      constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
+      const uint32_t kv_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sKV), Cfg::kKvPanelBytes);
+      uint32_t step = 0;
+      bool alive = true;
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
+        const QItem it = decode_q_item(p, idx);
+        if (!it.valid) continue;
+        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
+        const QSpans spans = make_q_spans(it, bs);
+        int active = 0;
+        for (int s = 0; s < plan.steps(); ++s) {
+          int kh, kt;
+          plan.step(s, kh, kt);
+          active += spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) != kTileSkip;
+        }
+        for (int j = 0; j < active; ++j, ++step) {
+          const uint32_t ks = Cfg::k_slot(step);
+          // the K tile arrived long ago (S of this step used it); this wait only orders our reads after the copy
+          if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 86)) { alive = false; break; }
+          if (!ptx::mbar_wait(ds_full, step & 1, abort_flag, 85)) { alive = false; break; }
           ptx::tc_fence_after();
           // dQ += dS K: the packed dS pieces of the compute warpgroups lie side by side, 8 columns per 16 keys
 #pragma unroll
           for (int kk = 0; kk < Cfg::kKeys / 16; ++kk) {
             ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDQ, tmem + Cfg::kTmemDS + kk * 8,
-                                kv_lo_mn + Cfg::k_slot(step) * (Cfg::kKvTileBytes >> 4) + kk * (2048 >> 4), kHi, idesc_g,
+                                kv_lo_mn + ks * (Cfg::kKvTileBytes >> 4) + kk * (2048 >> 4), kHi, idesc_g,
                                 (j > 0 || kk > 0) ? 1u : 0u);
           }
-          ptx::umma_commit(&kv_empty[Cfg::k_slot(step)]);
+          ptx::umma_commit(&kv_empty[ks]);
           ptx::umma_commit(ds_free);
         }
         if (!alive) break;
         ptx::umma_commit(q_empty);
         ptx::umma_commit(dq_full);
-        slot += active;
-        ++n_item;
       }
     }
   } else {
@@ -975,7 +1058,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     if (rc) return rc;
     const int items = p.tiles_per_half * 2 * p.heads * p.batch;
     const int grid = items < sm_count ? items : sm_count;
-    kernel<<<grid, kBwdThreads, Cfg::kSmemBytes, stream>>>(p);
+    kernel<<<grid, kBwdThreads + 32, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
   return FDA_OK;

@@ -221,21 +221,37 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
 // Debug build only: cost of a burst of MMAs issued by one thread of warp 16 while warps 0-15 make "noise" of one
 // kind: 0 idle (parked on a barrier), 1 polling an mbarrier that never completes, 2 FMA + ex2 arithmetic,
 // 3 shared-memory loads. out[noise] = cycles per MMA for SS N=128, out[4 + noise] for SS N=64, out[8 + noise] TS.
-__device__ long long g_contention[32];
-__global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
+__device__ long long g_contention[192];
+__device__ __align__(128) uint8_t g_copy_src[32768];
+__global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise, int random_fill, int out_base) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_never, bar_done;
+  __shared__ uint64_t bar_never, bar_done, bar_copy, bar_x, bar_y;
   __shared__ uint32_t tmem_base_s;
+  long long copies = 0;
   __shared__ int stop_flag, abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     stop_flag = 0; abort_flag = 0;
     ptx::mbar_init(&bar_never, 1);
     ptx::mbar_init(&bar_done, 1);
+    ptx::mbar_init(&bar_copy, 1);
+    ptx::mbar_init(&bar_x, 1);
+    ptx::mbar_init(&bar_y, 1);
     ptx::fence_mbar_init();
   }
   if (warp == 16) { ptx::tmem_alloc(&tmem_base_s, 512); ptx::tmem_relinquish(); }
+  if (random_fill) {
+    // bf16 values in (-1, 1) with busy mantissas, so that the tensor pipe toggles as it does on real data
+    uint32_t x = 0x9E3779B9u * (threadIdx.x + 1) + blockIdx.x;
+    for (int i = threadIdx.x; i < 196608 / 4; i += blockDim.x) {
+      x = x * 1664525u + 1013904223u;
+      const uint32_t lo16 = 0x3C00u + ((x >> 8) & 0x03FFu) + ((x >> 3) & 0x8000u);
+      const uint32_t hi16 = 0x3C00u + ((x >> 18) & 0x03FFu) + ((x >> 1) & 0x8000u);
+      reinterpret_cast<uint32_t*>(smem)[i] = lo16 | (hi16 << 16);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -257,7 +273,7 @@ __global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
         for (int i = 0; i < 8; ++i) { const float4 v = src[i * 512]; acc += v.x + v.w; }
       }
     }
-    else if (noise >= 4) {
+    else if (noise == 4 || noise == 5) {
       const uint32_t taddr = tmem + 384 + (static_cast<uint32_t>((warp & 3) * 32) << 16);
       uint32_t r[32];
       while (!*stop) {
@@ -267,7 +283,22 @@ __global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
         acc += __uint_as_float(r[lane]);
       }
     }
-    if (acc == 123.456f) g_contention[15] = 1;
+    else if (noise == 6 && threadIdx.x == 0) {
+      // bulk copies from global memory into a shared region the MMAs do not read, 32 KB per round
+      uint32_t par = 0;
+      long long t_start = clock64();
+      while (!*stop && clock64() - t_start < 400000000LL) {
+        ptx::mbar_expect_tx(&bar_copy, 32768);
+        ptx::bulk_load_1d(smem + 131072, g_copy_src, 16384, &bar_copy);
+        ptx::bulk_load_1d(smem + 131072 + 16384, g_copy_src + 16384, 16384, &bar_copy);
+        if (!ptx::mbar_wait(&bar_copy, par, &abort_flag, 111)) break;
+        par ^= 1;
+        ++copies;
+      }
+      if (blockIdx.x == 0) g_contention[out_base + 62] = copies;
+      if (blockIdx.x == 0) g_contention[out_base + 63] = clock64() - t_start;
+    }
+    if (acc == 123.456f) g_contention[191] = 1;
   } else if (lane == 0) {
     constexpr int kBurst = 256;
     const uint32_t hi = ptx::smem_desc_hi(1024);
@@ -289,7 +320,51 @@ __global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
       }
       ptx::umma_commit(&bar_done);
       ptx::mbar_wait(&bar_done, variant & 1, &abort_flag, 110);
-      g_contention[variant * 8 + noise] = (clock64() - t0) / kBurst;
+      if (blockIdx.x == 0) g_contention[out_base + variant * 8 + noise] = (clock64() - t0) / kBurst;
+    }
+    // Sequences of the backward kernels, operands stepping through the tiles as there. Variant 3: 16 SS N=64 (two
+    // chains over 8 k-steps) then 8 TS N=128 with an MN-major B; variant 4: 16 SS N=128 then 8 TS N=128.
+    for (int sync_pattern = 0; sync_pattern < 2; ++sync_pattern)
+    for (int variant = 3; variant < 5; ++variant) {
+      const uint32_t idesc_s = ptx::make_idesc(128, variant == 3 ? 64 : 128, 1, false, false);
+      const uint32_t idesc_g = ptx::make_idesc(128, 128, 1, false, true);
+      const uint32_t a2_lo = ptx::smem_desc_lo(ptx::smem_u32(smem + 65536), 16);
+      const uint32_t bpanel = variant == 3 ? 8192 : 16384;
+      const uint32_t b2_lo = ptx::smem_desc_lo(ptx::smem_u32(smem + 32768), 16);
+      const uint32_t b2_mn = ptx::smem_desc_lo(ptx::smem_u32(smem + 32768), bpanel);
+      constexpr int kRounds = 32;
+      const long long t0 = clock64();
+#pragma unroll 1
+      for (int i = 0; i < kRounds; ++i) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_off = ((kk / 4) * 16384 + (kk % 4) * 32) >> 4;
+          const uint32_t b_off = ((kk / 4) * bpanel + (kk % 4) * 32) >> 4;
+          ptx::umma_ss_f16_lh(tmem, a_lo + a_off, b2_lo + b_off, hi, idesc_s, kk > 0);
+          ptx::umma_ss_f16_lh(tmem + 128, a2_lo + a_off, b2_lo + b_off + ((variant == 3 ? 16384 : 32768) >> 4), hi, idesc_s, kk > 0);
+        }
+        const int nk = variant == 3 ? 4 : 8;
+        if (sync_pattern) {
+          ptx::umma_commit(&bar_x);
+          (void)ptx::mbar_try_wait(&bar_never, 0);
+          ptx::tc_fence_after();
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          if (kk < nk) {
+            ptx::umma_ts_f16_lh(tmem + 256, tmem + kk * 8, b2_mn + kk * (2048 >> 4), hi, idesc_g, 1);
+            if (variant == 3) ptx::umma_ts_f16_lh(tmem + 384, tmem + 128 + kk * 8, b2_mn + (16384 >> 4) + kk * (2048 >> 4), hi, idesc_g, 1);
+          }
+        }
+        if (sync_pattern) {
+          ptx::umma_commit(&bar_y);
+          (void)ptx::mbar_try_wait(&bar_never, 0);
+          ptx::tc_fence_after();
+        }
+      }
+      ptx::umma_commit(&bar_done);
+      ptx::mbar_wait(&bar_done, variant & 1, &abort_flag, 110);
+      if (blockIdx.x == 0) g_contention[out_base + (sync_pattern ? 48 : 24) + (variant - 3) * 8 + noise] = (clock64() - t0) / kRounds;
     }
     *stop = 1;
   }
@@ -302,13 +377,18 @@ __global__ void __launch_bounds__(544, 1) umma_contention_kernel(int noise) {
 }  // namespace
 
 #ifdef FDA_UMMA_TIMING
-extern "C" int fda_debug_umma_contention(long long* out16) {
+extern "C" int fda_debug_umma_contention(long long* out192) {
   cudaFuncSetAttribute(umma_contention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  for (int noise = 0; noise < 6; ++noise) {
-    umma_contention_kernel<<<1, 544, 200 * 1024>>>(noise);
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+  // one CTA on stale shared memory; one CTA on random data; one CTA per SM on random data
+  const int grids[3] = {1, 1, 148}, fills[3] = {0, 1, 1};
+  for (int cfg = 0; cfg < 3; ++cfg) {
+    for (int noise = 0; noise < 7; ++noise) {
+      if (cfg > 0 && noise != 0 && noise != 5) continue;
+      umma_contention_kernel<<<grids[cfg], 544, 200 * 1024>>>(noise, fills[cfg], cfg * 64);
+      if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    }
   }
-  return cudaMemcpyFromSymbol(out16, g_contention, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+  return cudaMemcpyFromSymbol(out192, g_contention, sizeof(long long) * 192) == cudaSuccess ? 0 : 1;
 }
 #endif
 
