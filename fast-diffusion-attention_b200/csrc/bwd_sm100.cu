@@ -36,9 +36,25 @@ __device__ long long g_fda_trace[8 * 256];
 extern "C" int fda_debug_trace(long long* out) {
   return cudaMemcpyFromSymbol(out, g_fda_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : 1;
 }
-#define FDA_TRACE_AT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
+#define FDA_TRACE_PUT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define FDA_TRACE_PUT(row, idx) do { } while (0)
+#endif
+// FDA_TRACE=1 traces the dK/dV kernel, FDA_TRACE=2 the dQ kernel
+#if defined(FDA_TRACE) && FDA_TRACE == 1
+#define FDA_TRACE_AT(row, idx) FDA_TRACE_PUT(row, idx)
 #else
 #define FDA_TRACE_AT(row, idx) do { } while (0)
+#endif
+#if defined(FDA_TRACE) && FDA_TRACE == 2
+#define FDA_TRACE_Q(row, idx) FDA_TRACE_PUT(row, idx)
+#else
+#define FDA_TRACE_Q(row, idx) do { } while (0)
+#endif
+#if defined(FDA_TRACE) && FDA_TRACE == 3   // item boundaries of the dQ kernel
+#define FDA_TRACE_QI(row, idx) FDA_TRACE_PUT(row, idx)
+#else
+#define FDA_TRACE_QI(row, idx) do { } while (0)
 #endif
 #ifdef FDA_CLOCKRATE
 __device__ unsigned long long g_fda_clockrate[2];
@@ -718,7 +734,15 @@ __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
 
 struct QSpans {
   Span half[2];  // key spans of the query tile per key half (0 noisy, 1 clean)
-  __device__ __forceinline__ int classify(int kh, int k0, int keys) const { return half[kh].classify(k0, keys); }
+  // selects instead of half[kh]: a run-time index would put the spans in local memory
+  __device__ __forceinline__ int classify(int kh, int k0, int keys) const {
+    Span s;
+    s.lo_first = kh ? half[1].lo_first : half[0].lo_first;
+    s.hi_first = kh ? half[1].hi_first : half[0].hi_first;
+    s.lo_last = kh ? half[1].lo_last : half[0].lo_last;
+    s.hi_last = kh ? half[1].hi_last : half[0].hi_last;
+    return s.classify(k0, keys);
+  }
 };
 
 __device__ __forceinline__ QSpans make_q_spans(const QItem& it, int bs) {
@@ -811,10 +835,12 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
         const QSpans spans = make_q_spans(it, bs);
         if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 71)) break;
+        FDA_TRACE_QI(6, n_item);
         ptx::mbar_expect_tx(q_full, 2 * T::kTileBytes);
         const int q_row = it.row0 + it.qh * it.n + it.qa;
         load_tile<kHeadDim>(sQ, &p.tm_q, q_full, q_row, it.h, it.bcoord);
         load_tile<kHeadDim>(sdO, &p.tm_do, q_full, q_row, it.h, it.bcoord);
+        FDA_TRACE_QI(7, n_item);
         for (int s = 0; s < plan.steps() && alive; ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
@@ -869,12 +895,14 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
           active += spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) != kTileSkip;
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
+        FDA_TRACE_QI(4, n_item);
         ++n_item;
         for (int j = 0; j < active; ++j, ++step) {
           const uint32_t ks = Cfg::k_slot(step), vs = Cfg::v_slot(step);
           if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) { alive = false; break; }
           if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) { alive = false; break; }
           if (!ptx::mbar_wait(sdp_free, (step & 1) ^ 1, abort_flag, 82)) { alive = false; break; }
+          FDA_TRACE_Q(3, step);
           ptx::tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
@@ -887,7 +915,11 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
           }
           ptx::umma_commit(sdp_full);
           ptx::umma_commit(&kv_empty[vs]);  // V tile no longer needed
+          FDA_TRACE_Q(4, step);
         }
+        // Q and dO are read by these products only: the tiles of the next item may load while the last dQ
+        // product and the epilogue of this one still run
+        if (alive) ptx::umma_commit(q_empty);
       }
     }
   } else if (warp == kMmaWarpB + 1) {
@@ -916,7 +948,9 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
           const uint32_t ks = Cfg::k_slot(step);
           // the K tile arrived long ago (S of this step used it); this wait only orders our reads after the copy
           if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 86)) { alive = false; break; }
+          FDA_TRACE_Q(0, step);
           if (!ptx::mbar_wait(ds_full, step & 1, abort_flag, 85)) { alive = false; break; }
+          FDA_TRACE_Q(1, step);
           ptx::tc_fence_after();
           // dQ += dS K: the packed dS pieces of the compute warpgroups lie side by side, 8 columns per 16 keys
 #pragma unroll
@@ -927,10 +961,11 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
           }
           ptx::umma_commit(&kv_empty[ks]);
           ptx::umma_commit(ds_free);
+          FDA_TRACE_Q(2, step);
         }
         if (!alive) break;
-        ptx::umma_commit(q_empty);
         ptx::umma_commit(dq_full);
+        FDA_TRACE_QI(5, n_sched);
       }
     }
   } else {
@@ -938,38 +973,64 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // query row inside the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint32_t n_item = 0, cnt = 0;
+    uint32_t n_item = 0, cnt = 0, n_sched = 0;
     bool alive = true;
-    for (uint32_t n_sched = 0; alive; ++n_sched) {
-      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
-      if (idx < 0 || idx >= total_items) break;
-      const QItem it = decode_q_item(p, idx);
-      if (!it.valid) continue;
-      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
-      const QSpans spans = make_q_spans(it, bs);
-      const int r = it.qa + row;
-      const bool row_valid = r < it.n;
-      const int r_eff = row_valid ? r : it.n - 1;
-      const int blk0 = block_lo(r_eff, bs);
-      const int blk1 = imin(blk0 + bs, it.n);
-      const int64_t seg = stat_segment(p, it.b, it.h, it.qh);
-      const float lse2 = p.lse2_pad[seg + r];
-      const float delta = p.delta_pad[seg + r];
-      for (int s = 0; s < plan.steps() && alive; ++s) {
+
+    // What a compute thread keeps of an item. The next item's record is filled while the last dQ product of the
+    // current one is still in the tensor pipe, so that its decode and its two statistics loads cost nothing. Two
+    // records alternate (no copies: they are meant to stay in registers).
+    struct ItemState {
+      KeyPlan plan;
+      QSpans spans;
+      int qh, blk0, blk1;
+      bool row_valid;
+      float lse2, delta;
+      uint16_t* dst;   // this thread's dQ row
+    };
+    auto fetch = [&](ItemState& t) -> bool {   // false: no more work (or a wait was abandoned)
+      for (;;) {
+        const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+        ++n_sched;
+        if (idx < 0 || idx >= total_items) return false;
+        const QItem it = decode_q_item(p, idx);
+        if (!it.valid) continue;
+        t.plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
+        t.spans = make_q_spans(it, bs);
+        t.qh = it.qh;
+        const int r = it.qa + row;
+        t.row_valid = r < it.n;
+        const int r_eff = t.row_valid ? r : it.n - 1;
+        t.blk0 = block_lo(r_eff, bs);
+        t.blk1 = imin(t.blk0 + bs, it.n);
+        const int64_t seg = stat_segment(p, it.b, it.h, it.qh);
+        t.lse2 = p.lse2_pad[seg + r];
+        t.delta = p.delta_pad[seg + r];
+        const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
+        t.dst = static_cast<uint16_t*>(p.dq) + it.bcoord * p.dq_bs + srow * p.dq_rs + it.h * p.dq_hs;
+        return true;
+      }
+    };
+
+    // One item: its steps, then the next item's record, then the epilogue. Returns whether `nxt` holds an item.
+    auto run_item = [&](const ItemState& cur, ItemState& nxt) -> bool {
+      if (threadIdx.x == 0) FDA_TRACE_QI(3, n_item);
+      for (int s = 0; s < cur.plan.steps() && alive; ++s) {
         int kh, kt;
-        plan.step(s, kh, kt);
+        cur.plan.step(s, kh, kt);
         constexpr int kKc = Cfg::kKeyCols;
-        const int cls = spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys);
+        const int cls = cur.spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys);
         if (cls == kTileSkip) continue;
         int lo = 0, hi = 0;
         if (cls == kTileMasked) {
-          if (it.qh == 1) { lo = 0; hi = blk1; }
-          else if (kh == 1) { lo = 0; hi = blk0; }
-          else { lo = blk0; hi = blk1; }
+          if (cur.qh == 1) { lo = 0; hi = cur.blk1; }
+          else if (kh == 1) { lo = 0; hi = cur.blk0; }
+          else { lo = cur.blk0; hi = cur.blk1; }
           lo -= kt * Cfg::kKeys + wg * kKc;
           hi -= kt * Cfg::kKeys + wg * kKc;
         }
+        if (threadIdx.x == 0) FDA_TRACE_Q(5, cnt);
         if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 91)) { alive = false; break; }
+        if (threadIdx.x == 0) FDA_TRACE_Q(6, cnt);
         ptx::tc_fence_after();
         uint32_t sv[kKc], dpv[kKc];
         if (kKc == 32) {
@@ -984,10 +1045,10 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
         ptx::mbar_arrive_warp(sdp_free);
         uint32_t pk_ds[kKc / 2];
         if (cls == kTileMasked) {
-          softmax_backward_cols<kKc, kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, lse2, delta,
+          softmax_backward_cols<kKc, kBf16, kSoftcap, false, true, false>(sv, dpv, nullptr, nullptr, cur.lse2, cur.delta,
                                                                           p.scale_log2, p.softcap_pre, lo, hi, nullptr, pk_ds);
         } else {
-          softmax_backward_cols<kKc, kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, lse2, delta,
+          softmax_backward_cols<kKc, kBf16, kSoftcap, false, false, false>(sv, dpv, nullptr, nullptr, cur.lse2, cur.delta,
                                                                            p.scale_log2, p.softcap_pre, 0, 0, nullptr, pk_ds);
         }
         if (!ptx::mbar_wait(ds_free, (cnt & 1) ^ 1, abort_flag, 92)) { alive = false; break; }
@@ -998,27 +1059,39 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(ds_full);
+        if (threadIdx.x == 0) FDA_TRACE_Q(7, cnt - 1);
       }
-      if (!alive) break;
-      if (!ptx::mbar_wait(dq_full, n_item & 1, abort_flag, 93)) break;
+      if (!alive) return false;
+      const bool have_next = fetch(nxt);
+      if (threadIdx.x == 0) FDA_TRACE_QI(2, n_item);
+      if (!ptx::mbar_wait(dq_full, n_item & 1, abort_flag, 93)) { alive = false; return false; }
+      if (threadIdx.x == 0) FDA_TRACE_QI(0, n_item);
       ++n_item;
       ptx::tc_fence_after();
-      {
-        const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
-        uint16_t* dst = static_cast<uint16_t*>(p.dq) + it.bcoord * p.dq_bs + srow * p.dq_rs + it.h * p.dq_hs;
-        constexpr int kChunks = kHeadDim / 32;  // 32-column chunks, dealt round-robin to the warpgroups
+      constexpr int kChunks = kHeadDim / 32;  // 32-column chunks, dealt round-robin to the warpgroups
 #pragma unroll
-        for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
-          const int gidx = g0 + wg;
-          if (gidx < kChunks) {
-            uint32_t acc[32];
-            ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + gidx * 32, acc);
-            ptx::tmem_wait_ld();
-            if (row_valid) ptx::store_row32<kBf16>(dst, gidx * 32, acc, p.softmax_scale, p.head_dim, p.wide_store != 0);
+      for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
+        const int gidx = g0 + wg;
+        if (gidx < kChunks) {
+          uint32_t acc[32];
+          ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + gidx * 32, acc);
+          ptx::tmem_wait_ld();
+          if (cur.row_valid) {
+            ptx::store_row32<kBf16>(cur.dst, gidx * 32, acc, p.softmax_scale, p.head_dim, p.wide_store != 0);
           }
         }
       }
+      if (threadIdx.x == 0) FDA_TRACE_QI(1, n_item - 1);
       ptx::tc_fence_before();
+      return have_next;
+    };
+
+    ItemState st0, st1;
+    bool have = fetch(st0);
+    while (have && alive) {
+      have = run_item(st0, st1);
+      if (!have || !alive) break;
+      have = run_item(st1, st0);
     }
   }
   ptx::tc_fence_before();

@@ -108,7 +108,15 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
 // without rows gets empty spans, so every key tile is "skip" for it.
 struct TileSpans {
   Span half[2];
-  __device__ __forceinline__ int classify(int kh, int kt) const { return half[kh].classify(kt * kBlockN, kBlockN); }
+  // selects instead of half[kh]: a run-time index would put the spans in local memory
+  __device__ __forceinline__ int classify(int kh, int kt) const {
+    Span s;
+    s.lo_first = kh ? half[1].lo_first : half[0].lo_first;
+    s.hi_first = kh ? half[1].hi_first : half[0].hi_first;
+    s.lo_last = kh ? half[1].lo_last : half[0].lo_last;
+    s.hi_last = kh ? half[1].hi_last : half[0].hi_last;
+    return s.classify(kt * kBlockN, kBlockN);
+  }
 };
 
 __device__ __forceinline__ TileSpans make_tile_spans(const Item& it, int t, int bs) {
@@ -137,7 +145,15 @@ struct FwdConfig {
   static constexpr int kStepElems = 32 / kElemBytes;                  // reduction elements per MMA (32 bytes)
   static constexpr int kPCols = kBlockN * kElemBytes / 4;             // tensor-memory columns of the packed P
   static_assert(kHeadDim % kPanelElems == 0, "head dimension must fill whole 128-byte panels");
-  static constexpr int kThreads = 128 * kQTiles + 64;
+  // Two query tiles: the two softmax warpgroups need more registers than an even split of the file gives them
+  // (168 per thread with the block rounded up to whole warpgroups), so the block is padded to three whole
+  // warpgroups and the third (TMA warp, MMA warp, two idle warps) hands most of its registers to the other two.
+  static constexpr bool kRegRealloc = kQTiles == 2;
+  static constexpr int kThreads = kRegRealloc ? 384 : 128 * kQTiles + 64;
+  static constexpr uint32_t kSoftmaxRegs = 216, kProducerRegs = 72;
+  // the pool is what the block got at launch, 384 threads x 168 registers: 2 * 128 * 216 + 128 * 72 = 384 * 168.
+  // Asking for more than the pool holds would block the warpgroup for ever.
+  static_assert(2 * 128 * kSoftmaxRegs + 128 * kProducerRegs <= 384 * 168, "register pool");
   static constexpr int kLoadWarp = 4 * kQTiles;
   static constexpr int kMmaWarp = 4 * kQTiles + 1;
   static constexpr int kSmemBytes = (kQTiles + kStages) * kTileBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
@@ -147,7 +163,7 @@ struct FwdConfig {
 };
 
 template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
-__global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
+__global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fwd_kernel(const __grid_constant__ FwdParams p) {
   using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -201,6 +217,10 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
   const uint32_t tmem = *tmem_slot;
   const int bs = p.block_size;
 
+  // The register counts are set inside the role branches: after a point where the branches meet again the
+  // compiler would have to assume the smaller count for everything.
+  if (warp >= 4 * kQTiles) {
+  if (Cfg::kRegRealloc) ptx::reg_release_to<Cfg::kProducerRegs>();
   if (warp == Cfg::kLoadWarp) {
     // ------------------------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -344,8 +364,10 @@ __global__ void __launch_bounds__(128 * kQTiles + 64, 1) fwd_kernel(const __grid
         ++n_item;
       }
     }
+  }
   } else {
     // ------------------------------------------------------------------------------------ softmax + epilogue
+    if (Cfg::kRegRealloc) ptx::reg_acquire_to<Cfg::kSoftmaxRegs>();
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int quad = warp & 3;                     // tensor-memory lane quadrant of this warp
     const int row = quad * 32 + lane;              // row inside the tile

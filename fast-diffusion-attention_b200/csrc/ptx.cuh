@@ -138,6 +138,19 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
       : "memory");
 }
 
+// ---- register reallocation between warpgroups -------------------------------------------------------------
+// Every warp of a warpgroup (four consecutive warps, the first a multiple of four) must execute the call; kRegs
+// is a multiple of 8 in [24, 256]. A kernel that uses these is launched with whole warpgroups only, and the
+// per-warpgroup counts it sets must add up to at most the 64K registers of the SM.
+template <uint32_t kRegs>
+__device__ __forceinline__ void reg_release_to() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <uint32_t kRegs>
+__device__ __forceinline__ void reg_acquire_to() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---- tensor memory ----------------------------------------------------------------------------------------
 // Whole-warp calls. `ncols` is a power of two >= 32; the address of the allocation is written to *smem_dst.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
