@@ -209,7 +209,11 @@ __device__ __forceinline__ void mma_rows_x_rows(uint32_t d_tmem, uint32_t a_lo, 
 constexpr int kCmpWG = 4;
 constexpr int kCols = kTile / kCmpWG;             // 32 columns per warpgroup
 constexpr int kCmpThreads = 128 * kCmpWG;         // 512
-constexpr int kBwdThreads = kCmpThreads + 64;     // + TMA warp + MMA warp
+constexpr int kBwdThreads = kCmpThreads + 128;    // + a warpgroup of TMA warp, two MMA warps and an idle warp
+// 640 threads start with 96 registers each; that pool is all the block ever has (asking for more would block a
+// warpgroup for ever): 4 * 128 * 104 + 128 * 64 = 640 * 96.
+constexpr uint32_t kComputeRegs = 104, kProducerRegs = 64;
+static_assert(kCmpThreads * kComputeRegs + 128 * kProducerRegs <= kBwdThreads * 96, "register pool");
 constexpr int kLoadWarpB = 4 * kCmpWG;
 constexpr int kMmaWarpB = 4 * kCmpWG + 1;
 static_assert(kCols == 32, "one 32-column tensor-memory load per operand and warp");
@@ -330,7 +334,7 @@ struct DkdvCfg {
   static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64], header
   static constexpr int kHeaderOffset = 2 * kSubTileBytes + 512;
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
-  static constexpr int kThreads = kBwdThreads + 32;  // a second MMA-issuing warp
+  static constexpr int kThreads = kBwdThreads;
   // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
   // head dimensions above 128 do not leave room for both accumulators next to the S^T / dP^T buffers: the key
   // tile is then processed in kPasses passes, each producing kAccDim columns of dK and dV
@@ -349,7 +353,7 @@ struct SubStep {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DkdvCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -432,6 +436,11 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dkdv_kernel(const __g
     return true;
   };
 
+  // Whole warpgroups: four of compute warps, one of the TMA warp, the two MMA warps and an idle warp. The fifth
+  // hands registers to the other four. The counts are set inside the role branches, so that the compiler never
+  // has to assume the smaller one where the branches meet.
+  if (warp >= 4 * kCmpWG) {
+  ptx::reg_release_to<kProducerRegs>();
   if (warp == kLoadWarpB) {
     // ------------------------------------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -585,7 +594,9 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dkdv_kernel(const __g
         ptx::umma_commit(acc_full);
       }
     }
+  }
   } else {
+    ptx::reg_acquire_to<kComputeRegs>();
     // ------------------------------------------------------------------------- softmax backward + epilogue
     const int wg = warp >> 2;                  // which kSubCols query columns of a sub-tile
     const int quad = warp & 3;
@@ -773,7 +784,7 @@ struct DqCfg {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DqCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -823,6 +834,11 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
   const int bs = p.block_size;
   const int total_items = p.tiles_per_half * 2 * p.heads * p.batch;
 
+  // Whole warpgroups: four of compute warps, one of the TMA warp, the two MMA warps and an idle warp. The fifth
+  // hands registers to the other four. The counts are set inside the role branches, so that the compiler never
+  // has to assume the smaller one where the branches meet.
+  if (warp >= 4 * kCmpWG) {
+  ptx::reg_release_to<kProducerRegs>();
   if (warp == kLoadWarpB) {
     if (lane == 0) {
       uint32_t n_item = 0, slot = 0;
@@ -968,7 +984,9 @@ __global__ void __launch_bounds__(kBwdThreads + 32, 1) bwd_dq_kernel(const __gri
         FDA_TRACE_QI(5, n_sched);
       }
     }
+  }
   } else {
+    ptx::reg_acquire_to<kComputeRegs>();
     const int wg = warp >> 2;                  // which kCols key columns
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // query row inside the tile
@@ -1131,7 +1149,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     if (rc) return rc;
     const int items = p.tiles_per_half * 2 * p.heads * p.batch;
     const int grid = items < sm_count ? items : sm_count;
-    kernel<<<grid, kBwdThreads + 32, Cfg::kSmemBytes, stream>>>(p);
+    kernel<<<grid, kBwdThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
   return FDA_OK;
