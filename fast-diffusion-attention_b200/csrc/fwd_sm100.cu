@@ -26,6 +26,32 @@
 #include "ptx.cuh"
 #include "sched.cuh"
 
+#ifdef FDA_TRACE
+__device__ long long g_fda_trace_f[8 * 256];
+extern "C" int fda_debug_trace_fwd(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fda_trace_f, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : 1;
+}
+#define FDA_TRACE_PUTF(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace_f[(row) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define FDA_TRACE_PUTF(row, idx) do { } while (0)
+#endif
+// FDA_TRACE=9: steps of the forward kernel; FDA_TRACE=8: its item boundaries
+#if defined(FDA_TRACE) && FDA_TRACE == 9
+#define FDA_TRACE_F(row, idx) FDA_TRACE_PUTF(row, idx)
+#else
+#define FDA_TRACE_F(row, idx) do { } while (0)
+#endif
+#if defined(FDA_TRACE) && FDA_TRACE == 8
+#define FDA_TRACE_FI(row, idx) FDA_TRACE_PUTF(row, idx)
+#else
+#define FDA_TRACE_FI(row, idx) do { } while (0)
+#endif
+#if defined(FDA_TRACE) && FDA_TRACE == 7   // inside the epilogue
+#define FDA_TRACE_FE(row, idx) FDA_TRACE_PUTF(row, idx)
+#else
+#define FDA_TRACE_FE(row, idx) do { } while (0)
+#endif
+
 namespace fda {
 namespace {
 
@@ -47,6 +73,8 @@ constexpr bool kUseMufuLock = FDA_MUFU_LOCK != 0;  // turn-taking of the two sof
 
 struct FwdParams {
   CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_o;    // out, boxes of 64 columns x 32 rows (used when o_tma != 0)
+  int o_tma;           // out's strides allow tile stores
   void* out;
   float* lse;
   int64_t o_batch_stride, o_row_stride, o_head_stride;
@@ -133,6 +161,15 @@ __device__ __forceinline__ TileSpans make_tile_spans(const Item& it, int t, int 
   return ts;
 }
 
+// What the roles need to know about an item. The TMA warp works it out once (that is where the divisions by the
+// block size and the head counts happen) and leaves it in shared memory next to the scheduler's mailbox; the MMA
+// thread and the softmax warps copy it from there.
+struct ItemDesc {
+  Item it;
+  KeyPlan plan;
+  TileSpans spans[2];
+};
+
 template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
 struct FwdConfig {
   // kType: 0 bf16, 1 fp16, 2 fp8 e4m3 (forward only; the output is bf16)
@@ -156,7 +193,11 @@ struct FwdConfig {
   static_assert(2 * 128 * kSoftmaxRegs + 128 * kProducerRegs <= 384 * 168, "register pool");
   static constexpr int kLoadWarp = 4 * kQTiles;
   static constexpr int kMmaWarp = 4 * kQTiles + 1;
-  static constexpr int kSmemBytes = (kQTiles + kStages) * kTileBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  // epilogue staging: per query tile one [128 rows][64 columns] 16-bit tile, stored to out as a whole
+  static constexpr int kStageOBytes = kBlockM * 128;
+  static constexpr int kSmemBytes = (kQTiles + kStages) * kTileBytes + kQTiles * kStageOBytes +
+                                    1024 /*alignment slack*/ + 1024 /*barriers, mailbox, item descriptions*/;
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
   static constexpr int kTmemS = 0;                  // S_t at t*128
   static constexpr int kTmemO = 128 * kQTiles;      // O_t at kTmemO + t*kHeadDim
   static_assert(kTmemO + kQTiles * kHeadDim <= 512, "tensor memory budget");
@@ -169,7 +210,8 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + kQTiles * Cfg::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * Cfg::kTileBytes);
+  uint8_t* sStageO = sKV + kStages * Cfg::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStageO + kQTiles * Cfg::kStageOBytes);
   uint64_t* q_full = bars;                       // 1
   uint64_t* q_empty = bars + 1;                  // 1
   uint64_t* kv_full = bars + 2;                  // kStages
@@ -181,6 +223,8 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
   int* mufu_lock = reinterpret_cast<int*>(mbox + 1);  // one per warp quadrant (= SM sub-partition)
+  ItemDesc* desc = reinterpret_cast<ItemDesc*>(reinterpret_cast<uint8_t*>(bars) + 512);  // two slots
+  static_assert(2 * sizeof(ItemDesc) <= 512, "item descriptions");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -227,11 +271,26 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       uint32_t slot = 0, n_item = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
-        const int idx = sched_produce(mbox, n_sched, p.ticket, abort_flag);
-        if (idx < 0 || idx >= p.total_items) break;
+        const int idx = sched_take(mbox, n_sched, p.ticket, abort_flag);
+        if (idx < 0) break;
+        if (idx >= p.total_items) {
+          sched_publish(mbox, n_sched, idx);
+          break;
+        }
         const Item it = decode_item<kQTiles>(p, idx);
+        KeyPlan plan{};
+        {
+          ItemDesc& d = desc[n_sched & 1u];
+          d.it = it;
+          if (it.valid) {
+            plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
+            d.plan = plan;
+#pragma unroll
+            for (int t = 0; t < kQTiles; ++t) d.spans[t] = make_tile_spans(it, t, bs);
+          }
+        }
+        sched_publish(mbox, n_sched, idx);
         if (!it.valid) continue;
-        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
         const int steps = plan.steps();
         const int q_row = it.row0 + it.qh * it.n + it.qa;
         const int ntiles = ceil_div(it.qb - it.qa, kBlockM);
@@ -254,6 +313,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             if (s == 0 && which == 0) {
               // Q after the first K tile: the first MMA needs both, the previous item may still own Q.
               if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 12)) { alive = false; break; }
+              FDA_TRACE_FI(0, n_item);
               ptx::mbar_expect_tx(q_full, ntiles * Cfg::kTileBytes);
               for (int t = 0; t < ntiles; ++t) {
 #pragma unroll
@@ -309,16 +369,20 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       };
 
       for (uint32_t n_sched = 0; alive; ++n_sched) {
-        const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
+        const int idx = sched_peek(mbox, n_sched, abort_flag);
         if (idx < 0 || idx >= p.total_items) break;
-        const Item it = decode_item<kQTiles>(p, idx);
-        if (!it.valid) continue;
-        const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
-        const int steps = plan.steps();
+        FDA_TRACE_FI(2, n_item);
+        const Item it = desc[n_sched & 1u].it;
+        const KeyPlan plan = desc[n_sched & 1u].plan;
         TileSpans spans[kQTiles];
 #pragma unroll
-        for (int t = 0; t < kQTiles; ++t) spans[t] = make_tile_spans(it, t, bs);
+        for (int t = 0; t < kQTiles; ++t) spans[t] = desc[n_sched & 1u].spans[t];
+        sched_release<false>(mbox, n_sched);
+        if (!it.valid) continue;
+        const int steps = plan.steps();
+        FDA_TRACE_FI(3, n_item);
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 21)) { alive = false; break; }
+        FDA_TRACE_FI(4, n_item);
         bool pend[kQTiles], o_acc[kQTiles];
 #pragma unroll
         for (int t = 0; t < kQTiles; ++t) { pend[t] = false; o_acc[t] = false; }
@@ -338,6 +402,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           for (int t = 0; t < kQTiles; ++t) {
             if (pend[t]) {
               if (!ptx::mbar_wait(&p_full[t], cnt_p[t] & 1, abort_flag, 24)) { alive = false; break; }
+              FDA_TRACE_F(2 * t, cnt_p[t]);
               ++cnt_p[t];
               ptx::tc_fence_after();
               issue_pv(t, slot_v % kStages, o_acc[t]);
@@ -347,6 +412,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             if (s < steps && spans[t].classify(kh, kt) != kTileSkip) {
               issue_s(t, slot_k % kStages);
               ptx::umma_commit(&s_full[t]);
+              FDA_TRACE_F(2 * t + 1, cnt_p[t]);
               pend[t] = true;
             }
           }
@@ -360,6 +426,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         for (int t = 0; t < kQTiles; ++t) {
           if (it.qa + t * kBlockM < it.qb) ptx::umma_commit(&o_full[t]);
         }
+        FDA_TRACE_FI(1, n_item);
         slot += 2 * steps;
         ++n_item;
       }
@@ -376,6 +443,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
     const uint32_t tmem_o = tmem + Cfg::kTmemO + t * kHeadDim + lane_addr;
     uint32_t cnt_s = 0, cnt_o = 0;
     bool alive = true;
+    uint8_t* stage_o = sStageO + t * Cfg::kStageOBytes;
 #ifdef FDA_PHASE_CLOCKS
     long long ph_wait = 0, ph_ld = 0, ph_math = 0, ph_st = 0, ph_epi = 0, ph_steps = 0, ph_t = 0, ph_owait = 0, ph_pre = 0, ph_sched = 0, ph_setup = 0;
 #define FDA_PH(acc) do { const long long _n = clock64(); acc += _n - ph_t; ph_t = _n; } while (0)
@@ -385,15 +453,16 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 #endif
     for (uint32_t n_sched = 0; alive; ++n_sched) {
       FDA_PH(ph_pre);
-      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      const int idx = sched_peek(mbox, n_sched, abort_flag);
       FDA_PH(ph_sched);
       if (idx < 0 || idx >= p.total_items) break;
-      const Item it = decode_item<kQTiles>(p, idx);
+      const Item it = desc[n_sched & 1u].it;
+      const TileSpans spans = desc[n_sched & 1u].spans[t];
+      const KeyPlan plan = desc[n_sched & 1u].plan;
+      sched_release<true>(mbox, n_sched);
       if (!it.valid) continue;
       const int ta = it.qa + t * kBlockM;
       if (ta >= it.qb) continue;
-      const TileSpans spans = make_tile_spans(it, t, bs);
-      const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, kBlockN);
       const int steps = plan.steps();
       const int r = ta + row;                      // position in the half
       const bool row_valid = r < it.n;
@@ -424,6 +493,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       float l_run = 0.f;
       bool o_started = false;
       FDA_PH(ph_setup);
+      if (threadIdx.x == 0) FDA_TRACE_FI(7, cnt_o);
       for (int s = 0; s < steps && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
@@ -431,6 +501,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         if (cls == kTileSkip) continue;
         FDA_PH(ph_pre);
         if (!ptx::mbar_wait(&s_full[t], cnt_s & 1, abort_flag, 31)) { alive = false; break; }
+        if (row == 0) FDA_TRACE_F(4 + 2 * t, cnt_s);
         FDA_PH(ph_wait);
         ++cnt_s;
         ptx::tc_fence_after();
@@ -535,6 +606,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&p_full[t]);
+        if (row == 0) FDA_TRACE_F(5 + 2 * t, cnt_s - 1);
         o_started = true;
         FDA_PH(ph_st);
 #ifdef FDA_PHASE_CLOCKS
@@ -545,12 +617,61 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       // ---- epilogue: O / l -> global, LSE
       FDA_PH(ph_pre);
       if (!ptx::mbar_wait(&o_full[t], cnt_o & 1, abort_flag, 32)) { alive = false; break; }
+      if (threadIdx.x == 0) FDA_TRACE_FI(5, cnt_o);
       FDA_PH(ph_owait);
       ++cnt_o;
       ptx::tc_fence_after();
       const float inv_l = out_scale / l_run;
       const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
-      {
+      if (threadIdx.x == 0) FDA_TRACE_FE(0, cnt_o - 1);
+      bool lse_done = false;
+      auto store_lse = [&]() {
+        lse_done = true;
+        if (row_valid) {
+        const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
+        const float lse = (l_run > 0.f) ? m_ref * lse_scale + (__log2f(l_run) - kPShift) * kLn2 : -INFINITY;
+        const int64_t li = (p.cu_seqlens != nullptr)
+                               ? static_cast<int64_t>(it.h) * p.total + srow
+                               : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
+        p.lse[li] = lse;
+        }
+      };
+      if (p.o_tma != 0 && ta + kBlockM <= it.n) {
+        // Whole tile: through shared memory, 64 columns at a time, and out as tile copies, one per warp (32 rows),
+        // so that no warp waits for another. (A row per thread written straight to global memory costs one
+        // memory transaction per thread and instruction; for a 128 x 128 tile that is thousands of cycles in
+        // which the load/store unit serves nobody else.)
+        uint8_t* my_stage = stage_o + quad * (32 * 128);
+#pragma unroll
+        for (int pass = 0; pass < kHeadDim / 64; ++pass) {
+          if (pass * 64 < p.head_dim) {
+            uint32_t o[64];
+            ptx::tmem_ld32(tmem_o + pass * 64, o);
+            ptx::tmem_ld32(tmem_o + pass * 64 + 32, o + 32);
+            ptx::tmem_wait_ld();
+            if (threadIdx.x == 0) FDA_TRACE_FE(1 + 3 * pass, cnt_o - 1);
+            uint32_t w[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              w[i] = ptx::pack2<kType != 1>(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
+            }
+            // the previous copy out of this warp's buffer (last pass or last item) must have read it completely
+            if (lane == 0) ptx::bulk_wait_group_read0();
+            __syncwarp();
+            if (threadIdx.x == 0) FDA_TRACE_FE(2 + 3 * pass, cnt_o - 1);
+            ptx::st_shared_row128_sw(my_stage, lane, w);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_4d(&p.tm_o, my_stage, pass * 64, it.row0 + it.qh * it.n + ta + quad * 32, it.h, it.bcoord);
+              ptx::bulk_commit_group();
+            }
+            if (threadIdx.x == 0) FDA_TRACE_FE(3 + 3 * pass, cnt_o - 1);
+            // the log-sum-exp goes out while the tile copy reads the buffer
+            if (!lse_done) store_lse();
+          }
+        }
+      } else {
         uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + it.bcoord * p.o_batch_stride + srow * p.o_row_stride +
                          it.h * p.o_head_stride;
         // all loads first, one wait: the stores of a chunk then overlap the conversion of the next
@@ -570,17 +691,14 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           }
         }
       }
-      if (row_valid) {
-        const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
-        const float lse = (l_run > 0.f) ? m_ref * lse_scale + (__log2f(l_run) - kPShift) * kLn2 : -INFINITY;
-        const int64_t li = (p.cu_seqlens != nullptr)
-                               ? static_cast<int64_t>(it.h) * p.total + srow
-                               : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
-        p.lse[li] = lse;
-      }
+      if (!lse_done) store_lse();
       ptx::tc_fence_before();
+      if (threadIdx.x == 0) FDA_TRACE_FE(7, cnt_o - 1);
       FDA_PH(ph_epi);
+      if (threadIdx.x == 0) FDA_TRACE_FI(6, cnt_o - 1);
     }
+    // shared memory must outlive the tile copies that read it
+    if (lane == 0) ptx::bulk_wait_group0();
 #ifdef FDA_PHASE_CLOCKS
     if (threadIdx.x == 0) {
       atomicAdd(&g_fda_phase[8], (unsigned long long)ph_sched);
@@ -675,6 +793,14 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
       p.descale_bs[i] = a.descale_batch_stride[i];
       p.descale_hs[i] = a.descale_head_stride[i];
     }
+  }
+  {
+    // out: 16-bit whatever the inputs are. Strides that do not suit a tile copy are not an error: the kernel
+    // then writes rows directly.
+    const int orc = encode_tile_map(&p.tm_o, a.out.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.out.row_stride,
+                                    a.out.head_stride, a.out.batch_stride, 64, 32);
+    if (orc != FDA_OK && orc != FDA_ERR_STRIDE) return orc;
+    p.o_tma = orc == FDA_OK ? 1 : 0;
   }
   p.out = a.out.ptr;
   p.lse = a.lse;

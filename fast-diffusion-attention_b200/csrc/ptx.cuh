@@ -138,6 +138,41 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
       : "memory");
 }
 
+// ---- tile stores through shared memory ----------------------------------------------------------------------
+// The tile lies in shared memory in the layout of the map (128-byte swizzle for the maps of this library); the
+// copy clips at the tensor's bounds. Generic-proxy writes to the tile need fence_proxy_async_smem() and a barrier
+// before the store is issued; the issuing thread commits a group and waits for it before the tile is reused.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2,
+                                             int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all committed groups of this thread have finished READING shared memory (the tile may be overwritten)
+__device__ __forceinline__ void bulk_wait_group_read0() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// all committed groups of this thread are complete
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(void* smem_dst, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_u32(smem_dst)), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+// Row `row` of a [rows][128 bytes] tile in the 128-byte swizzle: 16-byte chunk c of the row sits at chunk
+// c ^ (row & 7). `w` holds the row's 32 words (64 16-bit values).
+__device__ __forceinline__ void st_shared_row128_sw(uint8_t* tile, int row, const uint32_t* w) {
+  uint8_t* base = tile + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    st_shared_v4(base + ((c ^ (row & 7)) << 4), w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+  }
+}
+
 // ---- register reallocation between warpgroups -------------------------------------------------------------
 // Every warp of a warpgroup (four consecutive warps, the first a multiple of four) must execute the call; kRegs
 // is a multiple of 8 in [24, 256]. A kernel that uses these is launched with whole warpgroups only, and the

@@ -29,30 +29,50 @@ __device__ __forceinline__ void sched_init(SchedMailbox* m, int consumer_arrival
   }
 }
 
-// Producer side, one thread. `it` counts the items this CTA has taken (0, 1, 2, ...). Returns the item index
-// (>= total means "no more work"), or -1 if a wait was abandoned.
-__device__ __forceinline__ int sched_produce(SchedMailbox* m, uint32_t it, int* ticket, volatile int* abort_flag) {
+// Producer side, one thread, in two halves so that the producer can leave a description of the item in shared
+// memory (two slots, indexed like the mailbox: it & 1) before the consumers see the index. `it` counts the
+// items this CTA has taken (0, 1, 2, ...). sched_take returns the item index (>= total means "no more work"), or
+// -1 if a wait was abandoned; from then on slot it & 1 belongs to the producer until sched_publish.
+__device__ __forceinline__ int sched_take(SchedMailbox* m, uint32_t it, int* ticket, volatile int* abort_flag) {
   const uint32_t slot = it & 1u;
   if (!ptx::mbar_wait(&m->empty[slot], ((it >> 1) & 1u) ^ 1u, abort_flag, 5)) return -1;
-  const int v = (it == 0) ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(ticket, 1);
-  m->idx[slot] = v;
-  ptx::mbar_arrive(&m->full[slot]);  // release: the index is visible to whoever sees the phase complete
+  return (it == 0) ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(ticket, 1);
+}
+__device__ __forceinline__ void sched_publish(SchedMailbox* m, uint32_t it, int idx) {
+  const uint32_t slot = it & 1u;
+  m->idx[slot] = idx;
+  ptx::mbar_arrive(&m->full[slot]);  // release: the index and the description are visible to whoever sees the
+                                     // phase complete
+}
+__device__ __forceinline__ int sched_produce(SchedMailbox* m, uint32_t it, int* ticket, volatile int* abort_flag) {
+  const int v = sched_take(m, it, ticket, abort_flag);
+  if (v >= 0) sched_publish(m, it, v);
   return v;
 }
 
-// Consumer side. kWholeWarp: called by every lane of a consumer warp, lane 0 makes the arrival for the warp
-// after all lanes have read the slot. Otherwise: called by a single thread that makes its own arrival.
-template <bool kWholeWarp>
-__device__ __forceinline__ int sched_consume(SchedMailbox* m, uint32_t it, volatile int* abort_flag) {
+// Consumer side, also in two halves: sched_peek waits for item `it` and returns its index; the consumer may then
+// read the item's description; sched_release hands the slot back. kWholeWarp: called by every lane of a consumer
+// warp, lane 0 makes the arrival for the warp after all lanes are done with the slot. Otherwise: called by a
+// single thread that makes its own arrival.
+__device__ __forceinline__ int sched_peek(SchedMailbox* m, uint32_t it, volatile int* abort_flag) {
   const uint32_t slot = it & 1u;
   if (!ptx::mbar_wait(&m->full[slot], (it >> 1) & 1u, abort_flag, 6)) return -1;
-  const int v = m->idx[slot];
+  return m->idx[slot];
+}
+template <bool kWholeWarp>
+__device__ __forceinline__ void sched_release(SchedMailbox* m, uint32_t it) {
+  const uint32_t slot = it & 1u;
   if (kWholeWarp) {
     __syncwarp();
     if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(&m->empty[slot]);
   } else {
     ptx::mbar_arrive(&m->empty[slot]);
   }
+}
+template <bool kWholeWarp>
+__device__ __forceinline__ int sched_consume(SchedMailbox* m, uint32_t it, volatile int* abort_flag) {
+  const int v = sched_peek(m, it, abort_flag);
+  if (v >= 0) sched_release<kWholeWarp>(m, it);
   return v;
 }
 
