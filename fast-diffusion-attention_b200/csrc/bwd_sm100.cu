@@ -675,7 +675,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       ++n_item;
       ptx::tc_fence_after();
       {
-        const bool key_valid = kj < it.n;
+        const int rows_valid = imax(0, imin(32, it.n - (it.k0 + quad * 32)));  // of this warp's 32 key rows
         const int64_t srow = static_cast<int64_t>(it.row0) + it.kh * it.n + kj;
         uint16_t* dk_row = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
         uint16_t* dv_row = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
@@ -691,10 +691,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
             uint32_t accv[32];
             ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, accv);
             ptx::tmem_wait_ld();
-            if (key_valid) {
-              ptx::store_row32<kBf16>(is_dv ? dv_row : dk_row, col0, accv, is_dv ? 1.f : p.softmax_scale, p.head_dim,
-                                      p.wide_store != 0);
-            }
+            ptx::store_rows32_grouped<kBf16>(is_dv ? dv_row : dk_row, is_dv ? p.dv_rs : p.dk_rs, rows_valid, col0, accv,
+                                             is_dv ? 1.f : p.softmax_scale, p.head_dim);
           }
         }
       }
@@ -1001,7 +999,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
       KeyPlan plan;
       QSpans spans;
       int qh, blk0, blk1;
-      bool row_valid;
+      int rows_valid;   // of this warp's 32 query rows
       float lse2, delta;
       uint16_t* dst;   // this thread's dQ row
     };
@@ -1016,8 +1014,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         t.spans = make_q_spans(it, bs);
         t.qh = it.qh;
         const int r = it.qa + row;
-        t.row_valid = r < it.n;
-        const int r_eff = t.row_valid ? r : it.n - 1;
+        t.rows_valid = imax(0, imin(32, it.n - (it.qa + quad * 32)));
+        const int r_eff = r < it.n ? r : it.n - 1;
         t.blk0 = block_lo(r_eff, bs);
         t.blk1 = imin(t.blk0 + bs, it.n);
         const int64_t seg = stat_segment(p, it.b, it.h, it.qh);
@@ -1094,9 +1092,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           uint32_t acc[32];
           ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + gidx * 32, acc);
           ptx::tmem_wait_ld();
-          if (cur.row_valid) {
-            ptx::store_row32<kBf16>(cur.dst, gidx * 32, acc, p.softmax_scale, p.head_dim, p.wide_store != 0);
-          }
+          ptx::store_rows32_grouped<kBf16>(cur.dst, p.dq_rs, cur.rows_valid, gidx * 32, acc, p.softmax_scale, p.head_dim);
         }
       }
       if (threadIdx.x == 0) FDA_TRACE_QI(1, n_item - 1);

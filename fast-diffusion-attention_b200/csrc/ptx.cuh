@@ -446,5 +446,55 @@ __device__ __forceinline__ void store_row32(uint16_t* row_ptr, int col0, const u
   }
 }
 
+// The same 32 columns, but stored so that four neighbouring lanes write 64 contiguous bytes of ONE row: the four
+// lanes of a group first swap their 16-byte pieces (a 4 x 4 transpose by two rounds of shuffles), then lane j
+// stores piece j of each of the group's four rows. A warp instruction then touches 8 rows instead of 32, which is
+// what the load/store unit's cost goes by. Every lane of the warp must call this (shuffles); lane l holds row l
+// of the warp's 32 rows, of which the first `rows_valid` are written. `row_ptr` is the lane's own row, rows are
+// `row_stride` elements apart, and everything is 16-byte aligned.
+template <bool kBf16>
+__device__ __forceinline__ void store_rows32_grouped(uint16_t* row_ptr, int64_t row_stride, int rows_valid, int col0,
+                                                     const uint32_t* acc, float scale, int head_dim) {
+  const int lane = threadIdx.x & 31;
+  const int j = lane & 3;
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    w[i] = pack2<kBf16>(__uint_as_float(acc[2 * i]) * scale, __uint_as_float(acc[2 * i + 1]) * scale);
+  }
+  // round 1, partner lane ^ 1: even lanes give pieces 1 and 3, odd lanes pieces 0 and 2
+#pragma unroll
+  for (int k = 0; k < 4; k += 2) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t send = (j & 1) ? w[4 * k + q] : w[4 * (k + 1) + q];
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      if (j & 1) w[4 * k + q] = recv; else w[4 * (k + 1) + q] = recv;
+    }
+  }
+  // round 2, partner lane ^ 2: lanes 0, 1 give pieces 2 and 3, lanes 2, 3 pieces 0 and 1
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t send = (j & 2) ? w[4 * k + q] : w[4 * (k + 2) + q];
+      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 2);
+      if (j & 2) w[4 * k + q] = recv; else w[4 * (k + 2) + q] = recv;
+    }
+  }
+  // now w[4 * i ..] is piece j (columns col0 + 8 j .. + 8) of row (lane & ~3) + i
+  const int col = col0 + 8 * j;
+  if (col < head_dim) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = (lane & ~3) + i;
+      if (r < rows_valid) {
+        uint16_t* dst = row_ptr + static_cast<int64_t>(i - j) * row_stride + col;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      }
+    }
+  }
+}
+
 }  // namespace ptx
 }  // namespace fda
