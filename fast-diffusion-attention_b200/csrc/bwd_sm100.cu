@@ -122,58 +122,76 @@ __device__ __forceinline__ int64_t stat_segment(const BwdParams& p, int b, int h
 // ------------------------------------------------------------------------------------------------------------
 // 1. preprocess
 // ------------------------------------------------------------------------------------------------------------
+constexpr int kPreUnroll = 4;   // rows per thread group: more loads in flight, fewer and longer blocks
+
 template <bool kBf16, int kLanes>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const __grid_constant__ BwdParams p) {
   constexpr int kRowsPerWarp = 32 / kLanes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / kLanes, l = lane % kLanes;
-  const int r = (blockIdx.x * 8 + warp) * kRowsPerWarp + sub;  // position in the half, < n_pad
   const int hh = blockIdx.y;
   const int h = hh >> 1, half = hh & 1;
   const int b = blockIdx.z;
-  if (r >= p.n_pad) return;
   const Sample sm = sample_of(p, b);
   const int64_t seg = stat_segment(p, b, h, half);
-  float acc = 0.f;
-  const bool valid = r < sm.n;
-  int64_t srow = 0;
-  if (valid) {
-    srow = static_cast<int64_t>(sm.row0) + half * sm.n + r;
-    const uint16_t* o = static_cast<const uint16_t*>(p.out) + sm.bcoord * p.o_bs + srow * p.o_rs + h * p.o_hs;
-    const uint16_t* g = static_cast<const uint16_t*>(p.dout) + sm.bcoord * p.do_bs + srow * p.do_rs + h * p.do_hs;
-    for (int c = l * 8; c < p.head_dim; c += kLanes * 8) {
-      const uint4 a = *reinterpret_cast<const uint4*>(o + c);
-      const uint4 d = *reinterpret_cast<const uint4*>(g + c);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
-      const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+  // row u of this thread group: position in the half (rows >= n, up to n_pad, only get their padding values)
+  const int r0 = ((blockIdx.x * 8 + warp) * kPreUnroll) * kRowsPerWarp + sub;
+  float acc[kPreUnroll];
+  // head dimensions up to 8 * kLanes take one 16-byte piece of O and of dO per lane: all loads of the kPreUnroll rows
+  // are issued before the first use
+  uint4 ov[kPreUnroll], gv[kPreUnroll];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 fa, fd;
-        if (kBf16) {
-          fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
-          fd = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[i]));
-        } else {
-          fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
-          fd = __half22float2(*reinterpret_cast<const __half2*>(&dw[i]));
-        }
-        acc = fmaf(fa.x, fd.x, acc);
-        acc = fmaf(fa.y, fd.y, acc);
-      }
+  for (int u = 0; u < kPreUnroll; ++u) {
+    const int r = r0 + u * kRowsPerWarp;
+    acc[u] = 0.f;
+    ov[u] = make_uint4(0, 0, 0, 0);
+    gv[u] = make_uint4(0, 0, 0, 0);
+    if (r < sm.n && l * 8 < p.head_dim) {
+      const int64_t srow = static_cast<int64_t>(sm.row0) + half * sm.n + r;
+      const uint16_t* o = static_cast<const uint16_t*>(p.out) + sm.bcoord * p.o_bs + srow * p.o_rs + h * p.o_hs;
+      const uint16_t* g = static_cast<const uint16_t*>(p.dout) + sm.bcoord * p.do_bs + srow * p.do_rs + h * p.do_hs;
+      ov[u] = *reinterpret_cast<const uint4*>(o + l * 8);
+      gv[u] = *reinterpret_cast<const uint4*>(g + l * 8);
     }
   }
 #pragma unroll
-  for (int off = kLanes / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (l == 0) {
-    float lse2 = INFINITY;
-    if (valid) {
-      const int64_t li = (p.cu_seqlens != nullptr)
-                             ? static_cast<int64_t>(h) * p.total + srow
-                             : (static_cast<int64_t>(b) * p.heads + h) * p.seqlen + (half * sm.n + r);
-      const float lse = p.lse[li];
-      lse2 = (lse == -INFINITY) ? 0.f : lse * kLog2e;
+  for (int u = 0; u < kPreUnroll; ++u) {
+    const uint32_t aw[4] = {ov[u].x, ov[u].y, ov[u].z, ov[u].w};
+    const uint32_t dw[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 fa, fd;
+      if (kBf16) {
+        fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+        fd = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[i]));
+      } else {
+        fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+        fd = __half22float2(*reinterpret_cast<const __half2*>(&dw[i]));
+      }
+      acc[u] = fmaf(fa.x, fd.x, acc[u]);
+      acc[u] = fmaf(fa.y, fd.y, acc[u]);
     }
-    p.delta_pad[seg + r] = valid ? acc : 0.f;
-    p.lse2_pad[seg + r] = lse2;
+#pragma unroll
+    for (int off = kLanes / 2; off > 0; off >>= 1) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], off);
+  }
+  if (l == 0) {
+#pragma unroll
+    for (int u = 0; u < kPreUnroll; ++u) {
+      const int r = r0 + u * kRowsPerWarp;
+      if (r >= p.n_pad) continue;
+      const bool valid = r < sm.n;
+      float lse2 = INFINITY;
+      if (valid) {
+        const int64_t srow = static_cast<int64_t>(sm.row0) + half * sm.n + r;
+        const int64_t li = (p.cu_seqlens != nullptr)
+                               ? static_cast<int64_t>(h) * p.total + srow
+                               : (static_cast<int64_t>(b) * p.heads + h) * p.seqlen + (half * sm.n + r);
+        const float lse = p.lse[li];
+        lse2 = (lse == -INFINITY) ? 0.f : lse * kLog2e;
+      }
+      p.delta_pad[seg + r] = valid ? acc[u] : 0.f;
+      p.lse2_pad[seg + r] = lse2;
+    }
   }
 }
 
@@ -1274,7 +1292,7 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
 
   if (stage_mask & 1u) {
     const int lanes = d <= 64 ? 8 : (d <= 128 ? 16 : 32);
-    const int rows_per_block = 8 * (32 / lanes);
+    const int rows_per_block = 8 * (32 / lanes) * kPreUnroll;
     dim3 grid((p.n_pad + rows_per_block - 1) / rows_per_block, 2 * pr.heads, pr.batch);
     if (bf16) {
       if (lanes == 8) bwd_preprocess_kernel<true, 8><<<grid, 256, 0, stream>>>(p);
