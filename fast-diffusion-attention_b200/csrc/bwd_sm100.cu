@@ -212,17 +212,6 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, u
   }
 }
 
-// D[tmem, 128 x 128] = A[smem tile, rows x d] * B[smem tile, rows x d]^T, both K-major along d.
-// a_lo / b_lo are descriptor low words of the tiles (ptx::smem_desc_lo(addr, 16)).
-template <int kHeadDim>
-__device__ __forceinline__ void mma_rows_x_rows(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
-#pragma unroll
-  for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-    const uint32_t off = ((kk / 4) * TileCfg<kHeadDim>::kPanelBytes + (kk % 4) * 32) >> 4;
-    ptx::umma_ss_f16_lh(d_tmem, a_lo + off, b_lo + off, ptx::smem_desc_hi(1024), idesc, kk > 0);
-  }
-}
-
 // Compute warpgroups of the two backward kernels: each owns kCols of the 128 columns of S / dP (all 128 lanes).
 constexpr int kCmpWG = 4;
 constexpr int kCols = kTile / kCmpWG;             // 32 columns per warpgroup
@@ -235,21 +224,6 @@ static_assert(kCmpThreads * kComputeRegs + 128 * kProducerRegs <= kBwdThreads * 
 constexpr int kLoadWarpB = 4 * kCmpWG;
 constexpr int kMmaWarpB = 4 * kCmpWG + 1;
 static_assert(kCols == 32, "one 32-column tensor-memory load per operand and warp");
-
-// D[tmem, 128 x d] (+)= A[tmem, 128 x 128 as 16-bit] * B[smem tile, 128 rows x d] (B MN-major: rows are the
-// reduction dimension). The A operand was written by the compute warpgroups in kCmpWG pieces of kCols
-// reduction rows (kCols/2 packed columns each); piece w starts at a_tmem + w * piece_stride.
-template <int kHeadDim>
-__device__ __forceinline__ void mma_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t piece_stride,
-                                                uint32_t b_lo, uint32_t idesc, bool accumulate) {
-  // b_lo = ptx::smem_desc_lo(tile address, panel bytes): B is used MN-major, 16 reduction rows = 2048 bytes
-#pragma unroll
-  for (int kk = 0; kk < kTile / 16; ++kk) {
-    const uint32_t a = a_tmem + ((kk * 16) / kCols) * piece_stride + ((kk * 16) % kCols) / 2;
-    ptx::umma_ts_f16_lh(d_tmem, a, b_lo + kk * (2048 >> 4), ptx::smem_desc_hi(1024), idesc,
-                        (accumulate || kk > 0) ? 1u : 0u);
-  }
-}
 
 // P and dS of kN columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
 // lse2 / delta are per column (kPerColumn, read from shared memory) or per thread. kMasked is a template

@@ -628,12 +628,12 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       auto store_lse = [&]() {
         lse_done = true;
         if (row_valid) {
-        const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
-        const float lse = (l_run > 0.f) ? m_ref * lse_scale + (__log2f(l_run) - kPShift) * kLn2 : -INFINITY;
-        const int64_t li = (p.cu_seqlens != nullptr)
-                               ? static_cast<int64_t>(it.h) * p.total + srow
-                               : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
-        p.lse[li] = lse;
+          const float m_ref = (m_run == -INFINITY) ? 0.f : m_run;
+          const float lse = (l_run > 0.f) ? m_ref * lse_scale + (__log2f(l_run) - kPShift) * kLn2 : -INFINITY;
+          const int64_t li = (p.cu_seqlens != nullptr)
+                                 ? static_cast<int64_t>(it.h) * p.total + srow
+                                 : (static_cast<int64_t>(it.b) * p.heads + it.h) * p.seqlen + (it.qh * it.n + r);
+          p.lse[li] = lse;
         }
       };
       if (p.o_tma != 0 && ta + kBlockM <= it.n) {
