@@ -15,7 +15,8 @@ Metric: training-step TFLOPS on visible (query, key) pairs: 3.5 * 4 * pairs * d 
 The JSON line carries:
   value      device-resident inputs, CUDA-event time of K steps (max over ranks), aggregate over ranks
   e2e        same step through the public API with HOST (pinned) buffers: q, k, v, dO copied host->device and
-             out, dq, dk, dv copied device->host inside the timed region
+             out, dq, dk, dv copied device->host inside the timed region, every step; the copies of neighbouring
+             steps overlap the kernels (separate copy streams, two buffer sets)
   roofline   the kernel with the largest share of the step, timed live with CUDA events between the launches
   cpu_baseline   the CPU oracle (oracle/diffusion_oracle.py, a port of the reference's reference.py) on a bounded
              sample of the same workload, on this box's host cores (rank 0, N=1 only)
@@ -310,29 +311,62 @@ def main():
     # ---- end to end through the public API with host buffers ---------------------------------------------------------
     e2e = None
     if not args.skip_e2e:
-        outs_host = [torch.empty_like(t).pin_memory() for t in (host[0], host[0], host[1], host[2])]
-        dev_in = [torch.empty_like(t, device=dev) for t in host]
+        # Every step copies its inputs from pinned host memory and its results (out, dq, dk, dv) back to pinned host
+        # memory. The copies of neighbouring steps overlap the kernels: inputs go up on one stream, results come
+        # down on another, two sets of device and host buffers alternate, events carry the dependencies.
+        outs_host = [[torch.empty_like(t).pin_memory() for t in (host[0], host[0], host[1], host[2])] for _ in range(2)]
+        dev_in = [[torch.empty_like(t, device=dev) for t in host] for _ in range(2)]
+        s_main = torch.cuda.current_stream(dev)
+        s_up, s_down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        out_done = [torch.cuda.Event() for _ in range(2)]
+        computed = [torch.cuda.Event() for _ in range(2)]
+        e2e_count = [0]
 
         def step_e2e():
-            for dst, src in zip(dev_in, host):
-                dst.copy_(src, non_blocking=True)
-            qd, kd, vd, dod = dev_in
+            i = e2e_count[0]
+            e2e_count[0] += 1
+            slot = i & 1
+            with torch.cuda.stream(s_up):
+                if i >= 2:
+                    s_up.wait_event(in_free[slot])       # the step that last read these device inputs is done
+                for dst, src in zip(dev_in[slot], host):
+                    dst.copy_(src, non_blocking=True)
+                in_ready[slot].record(s_up)
+            s_main.wait_event(in_ready[slot])
+            qd, kd, vd, dod = dev_in[slot]
             qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
             out = diffusion_attn_func(qd, kd, vd, bs)
             gq, gk, gv = torch.autograd.grad(out, (qd, kd, vd), dod)
-            for dst, src in zip(outs_host, (out.detach(), gq, gk, gv)):
-                dst.copy_(src, non_blocking=True)
             qd.requires_grad_(False); kd.requires_grad_(False); vd.requires_grad_(False)
+            in_free[slot].record(s_main)
+            computed[slot].record(s_main)
+            results = (out.detach(), gq, gk, gv)
+            with torch.cuda.stream(s_down):
+                s_down.wait_event(computed[slot])
+                for dst, src in zip(outs_host[slot], results):
+                    src.record_stream(s_down)            # allocated on the main stream, read on this one
+                    dst.copy_(src, non_blocking=True)
+                out_done[slot].record(s_down)
+
+        def drain():
+            for e in out_done:
+                s_main.wait_event(e)
 
         for _ in range(3):
             step_e2e()
+        drain()
         barrier()
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(4, min(args.steps, 10))
         e_start.record()
+        s_up.wait_event(e_start)
         for _ in range(e2e_steps):
             step_e2e()
+        drain()
         e_end.record()
         barrier()
+        outs_host = outs_host[0]
         e2e_ms = max_over_ranks(e_start.elapsed_time(e_end), dist, world, dev) / e2e_steps
         e2e = dict(value=step_flops * world / (e2e_ms * 1e-3) / 1e12, unit="TFLOPS",
                    h2d_bytes_per_step=sum(t.numel() * 2 for t in host),
