@@ -534,6 +534,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           ptx::umma_commit(&sdp_full[u]);
           FDA_TRACE_AT(4, g);
         }
+        // K and V are read by these products only: the next item's tiles may load while the last dV / dK products
+        // and the epilogue of this item still run
+        if (alive) ptx::umma_commit(kv_empty);
         ++n_item;
       }
     }
@@ -582,7 +585,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
           FDA_TRACE_AT(2, g);
         }
         if (!alive) break;
-        ptx::umma_commit(kv_empty);
         ptx::umma_commit(acc_full);
       }
     }

@@ -419,9 +419,12 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           if (!alive) break;
           if (s > 0) ptx::umma_commit(&kv_empty[slot_v % kStages]);
           if (s < steps) ptx::umma_commit(&kv_empty[slot_k % kStages]);
+          // Q is read by the S products only: after the last of them the next item's Q may load, while the last
+          // P V products and the epilogue of this item still run
+          if (s == steps - 1) ptx::umma_commit(q_empty);
         }
         if (!alive) break;
-        ptx::umma_commit(q_empty);
+        if (steps == 0) ptx::umma_commit(q_empty);
 #pragma unroll
         for (int t = 0; t < kQTiles; ++t) {
           if (it.qa + t * kBlockM < it.qb) ptx::umma_commit(&o_full[t]);
