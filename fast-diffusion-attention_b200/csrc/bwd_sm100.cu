@@ -51,6 +51,11 @@ extern "C" int fda_debug_trace(long long* out) {
 #else
 #define FDA_TRACE_Q(row, idx) do { } while (0)
 #endif
+#if defined(FDA_TRACE) && FDA_TRACE == 4   // item boundaries of the dK/dV kernel
+#define FDA_TRACE_KI(row, idx) FDA_TRACE_PUT(row, idx)
+#else
+#define FDA_TRACE_KI(row, idx) do { } while (0)
+#endif
 #if defined(FDA_TRACE) && FDA_TRACE == 3   // item boundaries of the dQ kernel
 #define FDA_TRACE_QI(row, idx) FDA_TRACE_PUT(row, idx)
 #else
@@ -221,6 +226,13 @@ constexpr int kBwdThreads = kCmpThreads + 128;    // + a warpgroup of TMA warp, 
 // warpgroup for ever): 4 * 128 * 104 + 128 * 64 = 640 * 96.
 constexpr uint32_t kComputeRegs = 104, kProducerRegs = 64;
 static_assert(kCmpThreads * kComputeRegs + 128 * kProducerRegs <= kBwdThreads * 96, "register pool");
+// The dK/dV kernel has a sixth warpgroup that only writes the finished accumulators out, so that the compute
+// warps go straight on to the next item: 768 threads start with 80 registers each.
+constexpr int kDkdvThreads = kBwdThreads + 128;
+constexpr int kEpiWarp0 = 4 * kCmpWG + 4;
+constexpr uint32_t kDkdvComputeRegs = 88, kDkdvProducerRegs = 64, kDkdvEpilogueRegs = 64;
+static_assert(kCmpThreads * kDkdvComputeRegs + 128 * kDkdvProducerRegs + 128 * kDkdvEpilogueRegs <= kDkdvThreads * 80,
+              "register pool");
 constexpr int kLoadWarpB = 4 * kCmpWG;
 constexpr int kMmaWarpB = 4 * kCmpWG + 1;
 static_assert(kCols == 32, "one 32-column tensor-memory load per operand and warp");
@@ -326,7 +338,7 @@ struct DkdvCfg {
   static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q sub-tile, dO sub-tile, lse2[64], delta[64], header
   static constexpr int kHeaderOffset = 2 * kSubTileBytes + 512;
   static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 1024 + 512;
-  static constexpr int kThreads = kBwdThreads;
+  static constexpr int kThreads = kDkdvThreads;
   // buffer u: S^T at u*128, dP^T at u*128 + 64; accumulators behind
   // head dimensions above 128 do not leave room for both accumulators next to the S^T / dP^T buffers: the key
   // tile is then processed in kPasses passes, each producing kAccDim columns of dK and dV
@@ -345,7 +357,7 @@ struct SubStep {
 };
 
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
-__global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
+__global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DkdvCfg<kHeadDim, kStages>;
   using T = TileCfg<kHeadDim>;
   extern __shared__ uint8_t smem_raw[];
@@ -362,7 +374,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   uint64_t* pds_full = sdp_full + 2;         // [2]
   uint64_t* acc_full = pds_full + 2;
   uint64_t* buf_free = acc_full + 1;         // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(buf_free + 2);
+  uint64_t* acc_free = buf_free + 2;         // the epilogue warps have the accumulators in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
@@ -376,7 +389,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
 #endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 4 * kCmpWG + 2);
+    sched_init(mbox, 4 * kCmpWG + 2 + 4);   // compute warps, two MMA issuers, four epilogue warps
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -389,6 +402,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       ptx::mbar_init(&buf_free[u], 1);
     }
     ptx::mbar_init(acc_full, 1);
+    ptx::mbar_init(acc_free, 4);
     ptx::fence_mbar_init();
   }
   if (warp == kLoadWarpB) {
@@ -431,8 +445,53 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
   // Whole warpgroups: four of compute warps, one of the TMA warp, the two MMA warps and an idle warp. The fifth
   // hands registers to the other four. The counts are set inside the role branches, so that the compiler never
   // has to assume the smaller one where the branches meet.
-  if (warp >= 4 * kCmpWG) {
-  ptx::reg_release_to<kProducerRegs>();
+  if (warp >= kEpiWarp0) {
+    // ------------------------------------------------------------------------------------------------ epilogue
+    // Four warps, one per quarter of the tensor-memory lanes: dK and dV of a finished item go out to global memory
+    // while the other roles are already at work on the next item.
+    ptx::reg_release_to<kDkdvEpilogueRegs>();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    uint32_t n_item = 0;
+    for (uint32_t n_sched = 0;; ++n_sched) {
+      const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
+      if (idx < 0 || idx >= total_items) break;
+      const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
+      if (!it.valid) continue;
+      const int pass_col0 = (idx % Cfg::kPasses) * Cfg::kAccDim;
+      const int kj = it.k0 + row;
+      const int rows_valid = imax(0, imin(32, it.n - (it.k0 + quad * 32)));  // of this warp's 32 key rows
+      const int64_t srow = static_cast<int64_t>(it.row0) + it.kh * it.n + kj;
+      uint16_t* dk_row = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
+      uint16_t* dv_row = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
+      if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
+      ++n_item;
+      ptx::tc_fence_after();
+      // dK and dV sit side by side in tensor memory: 2 * d / 32 chunks of 32 columns
+      constexpr int kChunks = 2 * Cfg::kAccDim / 32;
+#pragma unroll 1
+      for (int gidx = 0; gidx < kChunks; ++gidx) {
+        const bool is_dv = gidx * 32 >= Cfg::kAccDim;
+        const int col0 = pass_col0 + gidx * 32 - (is_dv ? Cfg::kAccDim : 0);
+        uint32_t accv[32];
+        ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, accv);
+        ptx::tmem_wait_ld();
+        if (gidx == kChunks - 1) {
+          // everything is in registers: the first dV / dK products of the next item may overwrite the accumulators
+          ptx::tc_fence_before();
+          ptx::mbar_arrive_warp(acc_free);
+        }
+        // Plain row stores: these four warps are in nobody's way, what counts is that the accumulators are free
+        // again before the next item's first dV / dK product is due (a few thousand cycles).
+        if (lane < rows_valid) {
+          ptx::store_row32<kBf16>(is_dv ? dv_row : dk_row, col0, accv, is_dv ? 1.f : p.softmax_scale, p.head_dim,
+                                  p.wide_store != 0);
+        }
+      }
+    }
+  } else if (warp >= 4 * kCmpWG) {
+  ptx::reg_release_to<kDkdvProducerRegs>();
   if (warp == kLoadWarpB) {
     // ------------------------------------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -547,7 +606,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       const uint32_t idesc_g = ptx::make_idesc(kTile, Cfg::kAccDim, kFmt, false, true);
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
       const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), Cfg::kSubPanelBytes);    // MN-major use
-      uint32_t g = 0;
+      uint32_t g = 0, n_item_b = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_consume<false>(mbox, n_sched, abort_flag);
@@ -557,6 +616,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         // descriptor offset of the first 64-column panel of this pass in a sub-tile
         const uint32_t pass_panel_off = (idx % Cfg::kPasses) * (Cfg::kAccDim / 64) * (Cfg::kSubPanelBytes >> 4);
         bool acc = false;
+        // the first products of an item overwrite the accumulators: the epilogue warps must have read the last item's
+        if (!ptx::mbar_wait(acc_free, (n_item_b & 1u) ^ 1u, abort_flag, 57)) break;
+        ++n_item_b;
         for (bool last = false; alive && !last; ++g) {
           const uint32_t u = g & 1u, stage = g % kStages;
           // the stage barrier orders the header and, through the other issuer's wait on it, nothing else here:
@@ -590,8 +652,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     }
   }
   } else {
-    ptx::reg_acquire_to<kComputeRegs>();
-    // ------------------------------------------------------------------------- softmax backward + epilogue
+    ptx::reg_acquire_to<kDkdvComputeRegs>();
+    // -------------------------------------------------------------------------------------- softmax backward
     const int wg = warp >> 2;                  // which kSubCols query columns of a sub-tile
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // key row inside the tile
@@ -599,8 +661,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
     uint32_t n_item = 0, gc = 0;
     bool alive = true;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
+      if (threadIdx.x == 0) FDA_TRACE_KI(2, n_item);
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
       if (idx < 0 || idx >= total_items) break;
+      if (threadIdx.x == 0) FDA_TRACE_KI(3, n_item);
       const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
       const int pass_col0 = (idx % Cfg::kPasses) * Cfg::kAccDim;
       if (!it.valid) continue;
@@ -609,6 +673,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
       int same_lo, same_hi, cross_lo, cross_hi;
       query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
       query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
+      if (threadIdx.x == 0) FDA_TRACE_KI(4, n_item);
       for (bool last = false; alive && !last;) {
         const uint32_t u = gc & 1u, stage = gc % kStages;
         const uint8_t* stage_base = sStage + stage * Cfg::kStageBytes;
@@ -665,32 +730,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dkdv_kernel(const __grid_c
         if (threadIdx.x == 0) FDA_TRACE_AT(7, gc - 1);
       }
       if (!alive) break;
-      if (!ptx::mbar_wait(acc_full, n_item & 1, abort_flag, 62)) break;
       ++n_item;
-      ptx::tc_fence_after();
-      {
-        const int rows_valid = imax(0, imin(32, it.n - (it.k0 + quad * 32)));  // of this warp's 32 key rows
-        const int64_t srow = static_cast<int64_t>(it.row0) + it.kh * it.n + kj;
-        uint16_t* dk_row = static_cast<uint16_t*>(p.dk) + it.bcoord * p.dk_bs + srow * p.dk_rs + it.hk * p.dk_hs;
-        uint16_t* dv_row = static_cast<uint16_t*>(p.dv) + it.bcoord * p.dv_bs + srow * p.dv_rs + it.hk * p.dv_hs;
-        // dK and dV sit side by side in tensor memory: 2 * d / 32 chunks of 32 columns, dealt round-robin to the
-        // compute warpgroups
-        constexpr int kChunks = 2 * Cfg::kAccDim / 32;
-#pragma unroll
-        for (int g0 = 0; g0 < kChunks; g0 += kCmpWG) {
-          const int gidx = g0 + wg;
-          if (gidx < kChunks) {
-            const bool is_dv = gidx * 32 >= Cfg::kAccDim;
-            const int col0 = pass_col0 + gidx * 32 - (is_dv ? Cfg::kAccDim : 0);
-            uint32_t accv[32];
-            ptx::tmem_ld32(tmem + Cfg::kTmemDK + lane_addr + gidx * 32, accv);
-            ptx::tmem_wait_ld();
-            ptx::store_rows32_grouped<kBf16>(is_dv ? dv_row : dk_row, is_dv ? p.dv_rs : p.dk_rs, rows_valid, col0, accv,
-                                             is_dv ? 1.f : p.softmax_scale, p.head_dim);
-          }
-        }
-      }
-      ptx::tc_fence_before();
+      if (threadIdx.x == 0) FDA_TRACE_KI(5, n_item - 1);
     }
   }
   ptx::tc_fence_before();
