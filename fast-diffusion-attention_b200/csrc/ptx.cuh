@@ -452,16 +452,11 @@ __device__ __forceinline__ void store_row32(uint16_t* row_ptr, int col0, const u
 // what the load/store unit's cost goes by. Every lane of the warp must call this (shuffles); lane l holds row l
 // of the warp's 32 rows, of which the first `rows_valid` are written. `row_ptr` is the lane's own row, rows are
 // `row_stride` elements apart, and everything is 16-byte aligned.
-template <bool kBf16>
-__device__ __forceinline__ void store_rows32_grouped(uint16_t* row_ptr, int64_t row_stride, int rows_valid, int col0,
-                                                     const uint32_t* acc, float scale, int head_dim) {
+// `w` holds the row's 32 columns already scaled and packed to 16 bits (16 words); it is overwritten.
+__device__ __forceinline__ void store_rows32_grouped_packed(uint16_t* row_ptr, int64_t row_stride, int rows_valid,
+                                                            int col0, uint32_t* w, int head_dim) {
   const int lane = threadIdx.x & 31;
   const int j = lane & 3;
-  uint32_t w[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    w[i] = pack2<kBf16>(__uint_as_float(acc[2 * i]) * scale, __uint_as_float(acc[2 * i + 1]) * scale);
-  }
   // round 1, partner lane ^ 1: even lanes give pieces 1 and 3, odd lanes pieces 0 and 2
 #pragma unroll
   for (int k = 0; k < 4; k += 2) {
@@ -494,6 +489,22 @@ __device__ __forceinline__ void store_rows32_grouped(uint16_t* row_ptr, int64_t 
       }
     }
   }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void pack_row32(const uint32_t* acc, float scale, uint32_t* w) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    w[i] = pack2<kBf16>(__uint_as_float(acc[2 * i]) * scale, __uint_as_float(acc[2 * i + 1]) * scale);
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void store_rows32_grouped(uint16_t* row_ptr, int64_t row_stride, int rows_valid, int col0,
+                                                     const uint32_t* acc, float scale, int head_dim) {
+  uint32_t w[16];
+  pack_row32<kBf16>(acc, scale, w);
+  store_rows32_grouped_packed(row_ptr, row_stride, rows_valid, col0, w, head_dim);
 }
 
 }  // namespace ptx
