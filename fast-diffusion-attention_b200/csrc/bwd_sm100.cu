@@ -61,11 +61,28 @@ extern "C" int fda_debug_trace(long long* out) {
 #else
 #define FDA_TRACE_QI(row, idx) do { } while (0)
 #endif
+#ifdef FDA_CTA_TIMES
+__device__ unsigned long long g_fda_cta_times_b[2 * 2 * 160];   // [kernel][start / end][CTA]
+extern "C" int fda_debug_cta_times_bwd(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fda_cta_times_b, sizeof(unsigned long long) * 640) == cudaSuccess ? 0 : 1;
+}
+#define FDA_CTA_STAMP(kernel, which) do { if (threadIdx.x == 0 && blockIdx.x < 160) { unsigned long long t_; \
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_fda_cta_times_b[(kernel) * 320 + (which) * 160 + blockIdx.x] = t_; } } while (0)
+#else
+#define FDA_CTA_STAMP(kernel, which) do { } while (0)
+#endif
 #ifdef FDA_CLOCKRATE
 __device__ unsigned long long g_fda_clockrate[2];
 extern "C" int fda_debug_clockrate(unsigned long long* out2) {
   return cudaMemcpyFromSymbol(out2, g_fda_clockrate, 16) == cudaSuccess ? 0 : 1;
 }
+#endif
+
+#ifndef FDA_SHORT8_KV
+#define FDA_SHORT8_KV 4   // eighths of a (sample, head)'s items that count as short: dK/dV kernel
+#endif
+#ifndef FDA_SHORT8_Q
+#define FDA_SHORT8_Q 1    // the same for the dQ kernel
 #endif
 
 namespace fda {
@@ -95,6 +112,7 @@ struct BwdParams {
   int batch, seqlen, total, heads, heads_k, head_dim, block_size;
   int n_pad;           // round_up(max n, 128)
   int tiles_per_half;  // n_pad / 128
+  int n_long_kv, n_long_q;  // of the 2 * tiles_per_half items of a (sample, head): how many count as long
   int* ticket_kv;      // work counters of the two persistent kernels, zeroed before each launch
   int* ticket_q;
   int wide_store;      // dq/dk/dv rows allow 32-byte stores
@@ -288,8 +306,8 @@ __device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
   // the noisy key tiles (one block of queries each) as filler.
   KvItem it;
   const int per_bh = 2 * p.tiles_per_half;
-  const int bh = idx / per_bh;
-  const int rem = idx - bh * per_bh;
+  int bh, rem;
+  two_phase_order(idx, per_bh, p.n_long_kv, p.batch * p.heads_k, bh, rem);
   it.kh = rem < p.tiles_per_half ? 1 : 0;
   const int kt = rem < p.tiles_per_half ? rem : rem - p.tiles_per_half;
   it.b = bh / p.heads_k;
@@ -380,6 +398,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  FDA_CTA_STAMP(0, 0);
 #ifdef FDA_CLOCKRATE
   long long cr_c0 = 0; unsigned long long cr_t0 = 0;
   if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -744,6 +763,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
     g_fda_clockrate[1] = t1 - cr_t0;
   }
 #endif
+  FDA_CTA_STAMP(0, 1);
   if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
@@ -759,8 +779,8 @@ __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
   // (sample, head)-major for L2 reuse of K / V; inside a head late query tiles first (they see the most keys).
   QItem it;
   const int per_bh = 2 * p.tiles_per_half;
-  const int bh = idx / per_bh;
-  const int rem = idx - bh * per_bh;
+  int bh, rem;
+  two_phase_order(idx, per_bh, p.n_long_q, p.batch * p.heads, bh, rem);
   it.qh = rem & 1;
   const int t_rev = rem >> 1;
   it.b = bh / p.heads;
@@ -840,6 +860,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  FDA_CTA_STAMP(1, 0);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kCmpWG + 2);
@@ -1145,6 +1166,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   }
   ptx::tc_fence_before();
   __syncthreads();
+  FDA_CTA_STAMP(1, 1);
   if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
@@ -1288,6 +1310,14 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   p.block_size = pr.block_size;
   p.n_pad = static_cast<int>(round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile));
   p.tiles_per_half = p.n_pad / kTile;
+  {
+    // dK/dV: the noisy key tiles (the second half of the ranks) are short; dQ: the shortest eighth (fractions
+    // found by measurement on the benchmark shape)
+    const int per_bh = 2 * p.tiles_per_half;
+    p.n_long_kv = per_bh - (FDA_SHORT8_KV * per_bh) / 8;
+    if (p.n_long_kv < 1) p.n_long_kv = 1;
+    p.n_long_q = per_bh - (FDA_SHORT8_Q * per_bh) / 8;
+  }
   const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * p.n_pad * 4, 256);
   p.delta_pad = static_cast<float*>(a.workspace);
   p.lse2_pad = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + one);

@@ -26,6 +26,12 @@
 #include "ptx.cuh"
 #include "sched.cuh"
 
+#ifdef FDA_CTA_TIMES
+__device__ unsigned long long g_fda_cta_times[2 * 160];
+extern "C" int fda_debug_cta_times_fwd(unsigned long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fda_cta_times, sizeof(unsigned long long) * 320) == cudaSuccess ? 0 : 1;
+}
+#endif
 #ifdef FDA_TRACE
 __device__ long long g_fda_trace_f[8 * 256];
 extern "C" int fda_debug_trace_fwd(long long* out) {
@@ -50,6 +56,10 @@ extern "C" int fda_debug_trace_fwd(long long* out) {
 #define FDA_TRACE_FE(row, idx) FDA_TRACE_PUTF(row, idx)
 #else
 #define FDA_TRACE_FE(row, idx) do { } while (0)
+#endif
+
+#ifndef FDA_SHORT8_FWD
+#define FDA_SHORT8_FWD 2   // eighths of a (sample, head)'s items that count as short
 #endif
 
 namespace fda {
@@ -81,6 +91,7 @@ struct FwdParams {
   const int32_t* cu_seqlens;
   int batch, seqlen, total, heads, heads_k, head_dim, block_size;
   int items_per_half;  // ceil(max n / rows per item)
+  int n_long;          // of the 2 * items_per_half items of a (sample, head): how many count as long
   int total_items;
   int* ticket;         // global work counter, zeroed before the launch
   int wide_store;      // rows of out allow 32-byte stores
@@ -106,8 +117,8 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
   // head the items with the most key tiles (late query rows) come first.
   Item it;
   const int per_bh = 2 * p.items_per_half;
-  const int bh = idx / per_bh;
-  const int rem = idx - bh * per_bh;
+  int bh, rem;
+  two_phase_order(idx, per_bh, p.n_long, p.batch * p.heads, bh, rem);
   it.qh = rem & 1;
   const int p_rev = rem >> 1;
   it.b = bh / p.heads;
@@ -228,6 +239,13 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef FDA_CTA_TIMES
+  if (threadIdx.x == 0 && blockIdx.x < 160) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_fda_cta_times[blockIdx.x] = t;
+  }
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -720,6 +738,13 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 
   ptx::tc_fence_before();
   __syncthreads();
+#ifdef FDA_CTA_TIMES
+  if (threadIdx.x == 0 && blockIdx.x < 160) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_fda_cta_times[160 + blockIdx.x] = t;
+  }
+#endif
   if (warp == Cfg::kLoadWarp) ptx::tmem_dealloc(tmem, 512);
 }
 #undef FDA_PH
@@ -825,6 +850,10 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   const int max_n = pr.seqlen / 2;
   p.items_per_half = ceil_div(max_n, q_tiles * kBlockM);
   p.total_items = p.items_per_half * 2 * pr.heads * pr.batch;
+  {
+    const int per_bh = 2 * p.items_per_half;
+    p.n_long = per_bh - (FDA_SHORT8_FWD * per_bh) / 8;   // the shortest eighths run at the end
+  }
   const bool softcap = pr.softcap > 0.f;
   if (softcap) {
     p.scale_log2 = pr.softcap * kLog2e;

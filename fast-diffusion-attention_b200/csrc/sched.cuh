@@ -29,6 +29,24 @@ __device__ __forceinline__ void sched_init(SchedMailbox* m, int consumer_arrival
   }
 }
 
+// Order of the items. Every group (a sample and head) has `per_group` items ranked longest first. Rank for rank the
+// groups follow each other (group-major), so that the CTAs running at the same time share a group's tiles in L2;
+// but the short items of ALL groups come after the long items of all groups: the kernel then ends on short
+// items, and the CTAs finish within one short item of each other instead of one long one.
+__device__ __forceinline__ void two_phase_order(int idx, int per_group, int n_long, int n_groups, int& group,
+                                                int& rank) {
+  const int long_total = n_long * n_groups;
+  if (idx < long_total) {
+    group = idx / n_long;
+    rank = idx - group * n_long;
+  } else {
+    const int j = idx - long_total;
+    const int n_short = per_group - n_long;   // > 0 here, or long_total would cover every index
+    group = j / n_short;
+    rank = n_long + (j - group * n_short);
+  }
+}
+
 // Producer side, one thread, in two halves so that the producer can leave a description of the item in shared
 // memory (two slots, indexed like the mailbox: it & 1) before the consumers see the index. `it` counts the
 // items this CTA has taken (0, 1, 2, ...). sched_take returns the item index (>= total means "no more work"), or
