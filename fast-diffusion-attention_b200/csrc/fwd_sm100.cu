@@ -52,6 +52,11 @@ extern "C" int fda_debug_trace_fwd(long long* out) {
 #else
 #define FDA_TRACE_FI(row, idx) do { } while (0)
 #endif
+#if defined(FDA_TRACE) && FDA_TRACE == 6   // the four warps of softmax warpgroup 0, step by step
+#define FDA_TRACE_FW(row, idx) FDA_TRACE_PUTF(row, idx)
+#else
+#define FDA_TRACE_FW(row, idx) do { } while (0)
+#endif
 #if defined(FDA_TRACE) && FDA_TRACE == 7   // inside the epilogue
 #define FDA_TRACE_FE(row, idx) FDA_TRACE_PUTF(row, idx)
 #else
@@ -523,6 +528,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         FDA_PH(ph_pre);
         if (!ptx::mbar_wait(&s_full[t], cnt_s & 1, abort_flag, 31)) { alive = false; break; }
         if (row == 0) FDA_TRACE_F(4 + 2 * t, cnt_s);
+        if (t == 0 && lane == 0) FDA_TRACE_FW(4 + quad, cnt_s);
         FDA_PH(ph_wait);
         ++cnt_s;
         ptx::tc_fence_after();
@@ -628,6 +634,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&p_full[t]);
         if (row == 0) FDA_TRACE_F(5 + 2 * t, cnt_s - 1);
+        if (t == 0 && lane == 0) FDA_TRACE_FW(quad, cnt_s - 1);
         o_started = true;
         FDA_PH(ph_st);
 #ifdef FDA_PHASE_CLOCKS
