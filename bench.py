@@ -40,7 +40,7 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch on this workload, from the ncu capture summarised in
 # profiles/c2_step_kernels_ncu.md (bytes)
-NCU_TRAFFIC_BYTES = {"fwd_kernel": 520.0e6, "bwd_dkdv_kernel": 788.1e6, "bwd_dq_kernel": 662.6e6,
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 550.7e6, "bwd_dkdv_kernel": 897.0e6, "bwd_dq_kernel": 677.7e6,
                      "bwd_preprocess_kernel": None}
 
 WORKLOAD = dict(name="C2 bf16 MHA fwd+bwd", batch=8, n=2048, heads=16, heads_k=16, head_dim=128, block_size=256)
