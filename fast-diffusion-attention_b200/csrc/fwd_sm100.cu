@@ -830,12 +830,12 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
     }
   }
   {
-    // out: 16-bit whatever the inputs are. Strides that do not suit a tile copy are not an error: the kernel
-    // then writes rows directly.
+    // out: 16-bit whatever the inputs are. What the tile copy wants of out (16-byte aligned base and strides) is
+    // also what the row stores of partial tiles need, so a refusal here is final.
     const int orc = encode_tile_map(&p.tm_o, a.out.ptr, 2, false, fp16, d, rows, pr.heads, tma_batch, a.out.row_stride,
                                     a.out.head_stride, a.out.batch_stride, 64, 32);
-    if (orc != FDA_OK && orc != FDA_ERR_STRIDE) return orc;
-    p.o_tma = orc == FDA_OK ? 1 : 0;
+    if (orc != FDA_OK) return orc;
+    p.o_tma = 1;
   }
   p.out = a.out.ptr;
   p.lse = a.lse;

@@ -9,8 +9,9 @@
  *  - Every sample is [noisy half (n rows) | clean half (n rows)], 2n rows. Batched tensors are
  *    (batch, 2n, heads, head_dim); packed ("varlen") tensors are (total, heads, head_dim) with
  *    cu_seqlens (batch + 1 int32 on the device) and batch strides ignored.
- *  - Strides are in ELEMENTS. The last dimension is contiguous. Row/head/batch strides of q, k, v (and of
- *    dout in the backward) must be multiples of 16 bytes because the kernels fetch tiles with TMA.
+ *  - Strides are in ELEMENTS. The last dimension is contiguous. Base pointers and row/head/batch strides of every
+ *    tensor (inputs and outputs) must be multiples of 16 bytes: the kernels move tiles with TMA and rows with
+ *    16-byte vector accesses. Anything else is refused with FDA_ERR_STRIDE.
  *  - All pointers are device pointers on the current CUDA device. The library allocates nothing: outputs and
  *    the workspace are the caller's. Work is enqueued on `stream` (a cudaStream_t); no host synchronisation.
  *  - Return value 0 = success, otherwise an FdaStatus; fda_strerror() gives the message. Messages of argument

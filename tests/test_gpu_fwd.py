@@ -141,3 +141,40 @@ def test_forward_padded_head_dims(bs, d):
     k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
     v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
     check_forward(q, k, v, bs)
+
+
+def _fwd_through_abi(q, k, v, out, lse, bs):
+    """fda_fwd called the way a foreign host would: raw pointers and element strides of caller-owned tensors."""
+    import ctypes as C
+    from fast_diffusion_attention import _lib
+    from fast_diffusion_attention.interface import _problem, _tensor_view
+    lib = _lib.load()
+    B, L = q.shape[0], q.shape[1]
+    args = _lib.FdaFwdArgs()
+    args.p = _problem(q, k, B, L, B * L, bs, q.shape[-1] ** -0.5, 0.0, 0, False, None)
+    args.q, args.k, args.v, args.out = (_tensor_view(t, False) for t in (q, k, v, out))
+    args.lse = lse.data_ptr()
+    nbytes = lib.fda_fwd_workspace_bytes(C.byref(args.p))
+    ws = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=q.device)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+    rc = lib.fda_fwd(C.byref(args), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+    torch.cuda.synchronize()
+    return rc
+
+
+def test_forward_into_a_strided_output_and_refusal_of_misaligned_ones():
+    """out may be a view into a larger buffer as long as base and strides are multiples of 16 bytes; the rest of
+    the buffer is left alone. Strides that are not are refused before anything is launched."""
+    from fast_diffusion_attention import _lib
+    torch.manual_seed(5)
+    B, n, H, d, bs = 2, 200, 3, 64, 24
+    q, k, v = (torch.randn(B, 2 * n, H, d, device=DEV, dtype=torch.bfloat16) for _ in range(3))
+    want = diffusion_attn_func(q, k, v, bs)
+    lse = torch.empty(B, H, 2 * n, device=DEV, dtype=torch.float32)
+    big = torch.full((B, 2 * n, H, d + 8), float("nan"), device=DEV, dtype=torch.bfloat16)
+    assert _fwd_through_abi(q, k, v, big[..., :d], lse, bs) == 0
+    assert _lib.device_status()[0] == 0
+    assert torch.equal(big[..., :d], want)
+    assert torch.isnan(big[..., d:].float()).all()
+    odd = torch.empty((B, 2 * n, H, d + 4), device=DEV, dtype=torch.bfloat16)
+    assert _fwd_through_abi(q, k, v, odd[..., :d], lse, bs) == 7   # FDA_ERR_STRIDE
