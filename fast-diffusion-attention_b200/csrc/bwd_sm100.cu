@@ -51,6 +51,11 @@ extern "C" int fda_debug_trace(long long* out) {
 #else
 #define FDA_TRACE_Q(row, idx) do { } while (0)
 #endif
+#if defined(FDA_TRACE) && FDA_TRACE == 5   // phases of a compute warp in the dK/dV kernel
+#define FDA_TRACE_KC(row, idx) FDA_TRACE_PUT(row, idx)
+#else
+#define FDA_TRACE_KC(row, idx) do { } while (0)
+#endif
 #if defined(FDA_TRACE) && FDA_TRACE == 4   // item boundaries of the dK/dV kernel
 #define FDA_TRACE_KI(row, idx) FDA_TRACE_PUT(row, idx)
 #else
@@ -703,9 +708,24 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
         hdr.x = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[0];
         hdr.y = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[1];
         last = (hdr.x & 1) != 0;
+        // The per-column statistics of this warp's 16 query columns come into registers now, as four 16-byte loads
+        // each, while the S^T / dP^T products are still running: scalar loads inside the arithmetic below queue
+        // up behind the operand fetches of the MMAs, which keep the shared-memory pipe busy.
+        float l2r[kSubCols], dlr[kSubCols];
+        {
+          const float4* l2v = reinterpret_cast<const float4*>(stats + wg * kSubCols);
+          const float4* dlv = reinterpret_cast<const float4*>(stats + kSub + wg * kSubCols);
+#pragma unroll
+          for (int i = 0; i < kSubCols / 4; ++i) {
+            const float4 a = l2v[i], b = dlv[i];
+            l2r[4 * i] = a.x; l2r[4 * i + 1] = a.y; l2r[4 * i + 2] = a.z; l2r[4 * i + 3] = a.w;
+            dlr[4 * i] = b.x; dlr[4 * i + 1] = b.y; dlr[4 * i + 2] = b.z; dlr[4 * i + 3] = b.w;
+          }
+        }
         if (threadIdx.x == 0) FDA_TRACE_AT(5, gc);
         if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) { alive = false; break; }
         if (threadIdx.x == 0) FDA_TRACE_AT(6, gc);
+        if (threadIdx.x == 0) FDA_TRACE_KC(0, gc);
         ++gc;
         ptx::tc_fence_after();
         const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
@@ -718,9 +738,10 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
 #else
         for (int i = 0; i < kSubCols; ++i) { sv[i] = i; dpv[i] = i; }
 #endif
+        if (threadIdx.x == 0) FDA_TRACE_KC(1, gc - 1);
         uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
-        const float* l2 = stats + wg * kSubCols;
-        const float* dl = stats + kSub + wg * kSubCols;
+        const float* l2 = l2r;
+        const float* dl = dlr;
 #if FDA_ABL >= 1
         for (int i = 0; i < kSubCols / 2; ++i) { pk_p[i] = sv[i]; pk_ds[i] = dpv[i]; }
         if (false) {
@@ -739,13 +760,16 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
         }
         // a warp overwrites only columns it has itself already loaded: its packed P^T / dS^T pieces go to the
         // start of its own kSubCols columns
+        if (threadIdx.x == 0) FDA_TRACE_KC(2, gc - 1);
 #if FDA_ABL < 2
         ptx::tmem_st8(st_t, pk_p);
         ptx::tmem_st8(dpt_t, pk_ds);
         ptx::tmem_wait_st();
 #endif
         ptx::tc_fence_before();
+        if (threadIdx.x == 0) FDA_TRACE_KC(3, gc - 1);
         ptx::mbar_arrive_warp(&pds_full[u]);
+        if (threadIdx.x == 0) FDA_TRACE_KC(4, gc - 1);
         if (threadIdx.x == 0) FDA_TRACE_AT(7, gc - 1);
       }
       if (!alive) break;
