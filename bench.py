@@ -172,7 +172,19 @@ def make_cpu_sample(threads=None):
     return run_once, fwd + bwd, desc
 
 
+def use_all_host_threads():
+    """The launcher for several ranks pins every process to one OpenMP thread; the CPU arm is meant to use the
+    cores this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_reference_run(seconds_budget=20.0):
+    use_all_host_threads()
     run_once, flops, desc = make_cpu_sample()
     run_once()  # warm-up (allocator, thread pool)
     times = []
@@ -188,6 +200,7 @@ def run_reference_arm(args, rank, world):
     """The reference's CPU implementation of the path (its reference.py, restated in oracle/) on the host cores."""
     if rank != 0:
         return
+    use_all_host_threads()
     run_once, flops, desc = make_cpu_sample()
     for _ in range(max(args.warmup, 0)):
         run_once()
