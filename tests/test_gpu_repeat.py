@@ -1,0 +1,64 @@
+"""The same inputs many times over: every role of the kernels (TMA warp, MMA issuers, compute and epilogue
+warpgroups) hands work to the others through barriers, and a missing dependency would show up as a result that
+changes with the timing of a run. Outputs and gradients must be bitwise the same in every repetition, on shapes
+that make the CTAs take many items each (item boundaries are where buffers change owners)."""
+
+import pytest
+import torch
+
+from fast_diffusion_attention import _lib, diffusion_attn_func, diffusion_attn_varlen_func
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _step(q, k, v, do, bs, cu=None, max_len=None, **kw):
+    q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    if cu is None:
+        out, lse = diffusion_attn_func(q, k, v, bs, return_attn_probs=True, **kw)
+    else:
+        out, lse = diffusion_attn_varlen_func(q, k, v, cu, cu, max_len, max_len, bs, return_attn_probs=True, **kw)
+    out.backward(do)
+    return out.detach(), lse.detach(), q.grad, k.grad, v.grad
+
+
+@pytest.mark.parametrize("heads,heads_k,d,bs,n,batch", [
+    (16, 16, 128, 256, 2048, 8),    # the benchmark shape: about 14 / 28 items per CTA
+    (8, 2, 128, 96, 1100, 3),       # grouped heads, masked tiles, partial last tile
+    (6, 6, 64, 32, 1500, 4),
+    (4, 4, 256, 128, 1024, 2),
+])
+def test_bitwise_stable_over_repetitions(heads, heads_k, d, bs, n, batch):
+    torch.manual_seed(7)
+    q = torch.randn(batch, 2 * n, heads, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(batch, 2 * n, heads_k, d, device=DEV, dtype=torch.bfloat16)
+    do = torch.randn_like(q)
+    first = _step(q, k, v, do, bs)
+    junk = torch.empty(64 << 20, device=DEV, dtype=torch.uint8)
+    for rep in range(8):
+        if rep % 2:
+            junk.random_(0, 255)   # other work in between shifts the timing and the cache state
+        again = _step(q, k, v, do, bs)
+        for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), again, first):
+            assert torch.equal(a, b), f"{name} changed in repetition {rep}"
+    torch.cuda.synchronize()
+    assert _lib.device_status()[0] == 0
+
+
+def test_bitwise_stable_varlen_with_softcap():
+    torch.manual_seed(8)
+    ns = [700, 64, 1300, 0, 257, 2048, 5, 900]
+    cu = torch.tensor([0] + list(torch.tensor([2 * x for x in ns]).cumsum(0)), device=DEV, dtype=torch.int32)
+    total = 2 * sum(ns)
+    q = torch.randn(total, 8, 128, device=DEV, dtype=torch.float16)
+    k = torch.randn(total, 4, 128, device=DEV, dtype=torch.float16)
+    v = torch.randn(total, 4, 128, device=DEV, dtype=torch.float16)
+    do = torch.randn_like(q)
+    first = _step(q, k, v, do, 80, cu=cu, max_len=2 * max(ns), softcap=15.0)
+    for rep in range(6):
+        again = _step(q, k, v, do, 80, cu=cu, max_len=2 * max(ns), softcap=15.0)
+        for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), again, first):
+            assert torch.equal(a, b), f"{name} changed in repetition {rep}"
+    torch.cuda.synchronize()
+    assert _lib.device_status()[0] == 0
