@@ -447,7 +447,7 @@ __device__ __forceinline__ void store_row32(uint16_t* row_ptr, int col0, const u
 }
 
 // The same 32 columns, but stored so that four neighbouring lanes write 64 contiguous bytes of ONE row: the four
-// lanes of a group first swap their 16-byte pieces (a 4 x 4 transpose by two rounds of shuffles), then lane j
+// lanes of a group first swap their 16-byte pieces (a 4 x 4 transpose by two exchanges of shuffles), then lane j
 // stores piece j of each of the group's four rows. A warp instruction then touches 8 rows instead of 32, which is
 // what the load/store unit's cost goes by. Every lane of the warp must call this (shuffles); lane l holds row l
 // of the warp's 32 rows, of which the first `rows_valid` are written. `row_ptr` is the lane's own row, rows are
@@ -457,7 +457,7 @@ __device__ __forceinline__ void store_rows32_grouped_packed(uint16_t* row_ptr, i
                                                             int col0, uint32_t* w, int head_dim) {
   const int lane = threadIdx.x & 31;
   const int j = lane & 3;
-  // round 1, partner lane ^ 1: even lanes give pieces 1 and 3, odd lanes pieces 0 and 2
+  // first exchange, partner lane ^ 1: even lanes give pieces 1 and 3, odd lanes pieces 0 and 2
 #pragma unroll
   for (int k = 0; k < 4; k += 2) {
 #pragma unroll
@@ -467,7 +467,7 @@ __device__ __forceinline__ void store_rows32_grouped_packed(uint16_t* row_ptr, i
       if (j & 1) w[4 * k + q] = recv; else w[4 * (k + 1) + q] = recv;
     }
   }
-  // round 2, partner lane ^ 2: lanes 0, 1 give pieces 2 and 3, lanes 2, 3 pieces 0 and 1
+  // second exchange, partner lane ^ 2: lanes 0, 1 give pieces 2 and 3, lanes 2, 3 pieces 0 and 1
 #pragma unroll
   for (int k = 0; k < 2; ++k) {
 #pragma unroll
