@@ -62,3 +62,20 @@ def test_bitwise_stable_varlen_with_softcap():
             assert torch.equal(a, b), f"{name} changed in repetition {rep}"
     torch.cuda.synchronize()
     assert _lib.device_status()[0] == 0
+
+
+def test_sm_margin_changes_the_grid_not_the_result():
+    """sm_margin leaves SMs free for other work (flash_api.cpp:168-170, :300-301 of the reference): fewer
+    persistent CTAs walk the same items, every output is still produced by one item in one fixed order."""
+    torch.manual_seed(9)
+    q = torch.randn(2, 2 * 900, 8, 128, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(2, 2 * 900, 4, 128, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(2, 2 * 900, 4, 128, device=DEV, dtype=torch.bfloat16)
+    do = torch.randn_like(q)
+    base = _step(q, k, v, do, 64)
+    for margin in (1, 20, 140, 1000):   # more than there are SMs leaves one CTA
+        got = _step(q, k, v, do, 64, sm_margin=margin)
+        for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), got, base):
+            assert torch.equal(a, b), f"{name} differs with sm_margin={margin}"
+    torch.cuda.synchronize()
+    assert _lib.device_status()[0] == 0
