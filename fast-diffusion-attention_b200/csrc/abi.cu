@@ -113,7 +113,8 @@ int fda_device_status(int32_t* out4) {
   if (e != cudaSuccess) return fda::note_cuda_error(e, "cudaDeviceSynchronize");
   int32_t tmp[4];
   out4[0] = out4[1] = out4[2] = out4[3] = 0;
-  int (*readers[3])(int32_t*) = {fda::read_status_fwd, fda::read_status_bwd, fda::read_status_selftest};
+  int (*readers[4])(int32_t*) = {fda::read_status_fwd, fda::read_status_bwd, fda::read_status_bwd_fused,
+                                   fda::read_status_selftest};
   for (auto reader : readers) {
     int rc = reader(tmp);
     if (rc) return rc;

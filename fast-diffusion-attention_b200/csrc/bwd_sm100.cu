@@ -22,130 +22,10 @@
 // Numerics kept from the reference: P = exp2(S*c - LSE2) from the saved LSE, dS = P * (dP - delta)
 // [* (1 - tanh^2) with softcap, before masking], P and dS rounded to the input dtype before the second GEMMs,
 // dK and dQ scaled by softmax_scale once at the end (mainloop_bwd...hpp:836-893, :1009).
-#include "geometry.h"
-#include "host_util.h"
-#include "ptx.cuh"
-#include "sched.cuh"
-
-#ifndef FDA_ABL
-#define FDA_ABL 0   // debug builds only: 1 skips the softmax-backward arithmetic, 2 also the tensor-memory traffic
-#endif
-
-#ifdef FDA_TRACE
-__device__ long long g_fda_trace[8 * 256];
-extern "C" int fda_debug_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_fda_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : 1;
-}
-#define FDA_TRACE_PUT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define FDA_TRACE_PUT(row, idx) do { } while (0)
-#endif
-// FDA_TRACE=1 traces the dK/dV kernel, FDA_TRACE=2 the dQ kernel
-#if defined(FDA_TRACE) && FDA_TRACE == 1
-#define FDA_TRACE_AT(row, idx) FDA_TRACE_PUT(row, idx)
-#else
-#define FDA_TRACE_AT(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 2
-#define FDA_TRACE_Q(row, idx) FDA_TRACE_PUT(row, idx)
-#else
-#define FDA_TRACE_Q(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 5   // phases of a compute warp in the dK/dV kernel
-#define FDA_TRACE_KC(row, idx) FDA_TRACE_PUT(row, idx)
-#else
-#define FDA_TRACE_KC(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 4   // item boundaries of the dK/dV kernel
-#define FDA_TRACE_KI(row, idx) FDA_TRACE_PUT(row, idx)
-#else
-#define FDA_TRACE_KI(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 3   // item boundaries of the dQ kernel
-#define FDA_TRACE_QI(row, idx) FDA_TRACE_PUT(row, idx)
-#else
-#define FDA_TRACE_QI(row, idx) do { } while (0)
-#endif
-#ifdef FDA_CTA_TIMES
-__device__ unsigned long long g_fda_cta_times_b[2 * 2 * 160];   // [kernel][start / end][CTA]
-extern "C" int fda_debug_cta_times_bwd(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_fda_cta_times_b, sizeof(unsigned long long) * 640) == cudaSuccess ? 0 : 1;
-}
-#define FDA_CTA_STAMP(kernel, which) do { if (threadIdx.x == 0 && blockIdx.x < 160) { unsigned long long t_; \
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); g_fda_cta_times_b[(kernel) * 320 + (which) * 160 + blockIdx.x] = t_; } } while (0)
-#else
-#define FDA_CTA_STAMP(kernel, which) do { } while (0)
-#endif
-#ifdef FDA_CLOCKRATE
-__device__ unsigned long long g_fda_clockrate[2];
-extern "C" int fda_debug_clockrate(unsigned long long* out2) {
-  return cudaMemcpyFromSymbol(out2, g_fda_clockrate, 16) == cudaSuccess ? 0 : 1;
-}
-#endif
-
-#ifndef FDA_SHORT8_KV
-#define FDA_SHORT8_KV 4   // eighths of a (sample, head)'s items that count as short: dK/dV kernel
-#endif
-#ifndef FDA_SHORT8_Q
-#define FDA_SHORT8_Q 1    // the same for the dQ kernel
-#endif
+#include "bwd_common.cuh"
 
 namespace fda {
 namespace {
-
-constexpr int kTile = 128;  // rows of every query / key tile
-constexpr float kLog2e = 1.4426950408889634f;
-
-struct BwdParams {
-  CUtensorMap tm_q, tm_k, tm_v, tm_do;
-  CUtensorMap tm_q64, tm_do64;  // same tensors, 64-row boxes (dK/dV kernel)
-  CUtensorMap tm_k64, tm_v64;   // 64-row boxes of K / V (dQ kernel for head dimensions above 128)
-  const void* out;
-  const void* dout;
-  void* dq;
-  void* dk;
-  void* dv;
-  int64_t o_bs, o_rs, o_hs;
-  int64_t do_bs, do_rs, do_hs;
-  int64_t dq_bs, dq_rs, dq_hs;
-  int64_t dk_bs, dk_rs, dk_hs;
-  int64_t dv_bs, dv_rs, dv_hs;
-  const float* lse;
-  float* delta_pad;  // (batch, heads, 2, n_pad)
-  float* lse2_pad;   // (batch, heads, 2, n_pad)
-  const int32_t* cu_seqlens;
-  int batch, seqlen, total, heads, heads_k, head_dim, block_size;
-  int n_pad;           // round_up(max n, 128)
-  int tiles_per_half;  // n_pad / 128
-  int n_long_kv, n_long_q;  // of the 2 * tiles_per_half items of a (sample, head): how many count as long
-  int* ticket_kv;      // work counters of the two persistent kernels, zeroed before each launch
-  int* ticket_q;
-  int wide_store;      // dq/dk/dv rows allow 32-byte stores
-  float scale_log2, softcap_pre, softmax_scale;
-};
-
-struct Sample {
-  int n, row0, bcoord;
-};
-
-__device__ __forceinline__ Sample sample_of(const BwdParams& p, int b) {
-  Sample s;
-  if (p.cu_seqlens != nullptr) {
-    const int lo = p.cu_seqlens[b];
-    s.n = (p.cu_seqlens[b + 1] - lo) / 2;
-    s.row0 = lo;
-    s.bcoord = 0;
-  } else {
-    s.n = p.seqlen / 2;
-    s.row0 = 0;
-    s.bcoord = b;
-  }
-  return s;
-}
-
-__device__ __forceinline__ int64_t stat_segment(const BwdParams& p, int b, int h, int half) {
-  return ((static_cast<int64_t>(b) * p.heads + h) * 2 + half) * p.n_pad;
-}
 
 // ------------------------------------------------------------------------------------------------------------
 // 1. preprocess
@@ -223,135 +103,9 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const __grid_consta
   }
 }
 
-// Shared-memory layout helpers ------------------------------------------------------------------------------------
-template <int kHeadDim>
-struct TileCfg {
-  static constexpr int kTileBytes = kTile * kHeadDim * 2;
-  static constexpr int kPanels = kHeadDim / 64;
-  static constexpr int kPanelBytes = 128 * 128;
-};
-
-template <int kHeadDim>
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int row, int head,
-                                          int bcoord) {
-#pragma unroll
-  for (int c = 0; c < TileCfg<kHeadDim>::kPanels; ++c) {
-    ptx::tma_load_4d(dst + c * TileCfg<kHeadDim>::kPanelBytes, tm, bar, c * 64, row, head, bcoord);
-  }
-}
-
-// Compute warpgroups of the two backward kernels: each owns kCols of the 128 columns of S / dP (all 128 lanes).
-constexpr int kCmpWG = 4;
-constexpr int kCols = kTile / kCmpWG;             // 32 columns per warpgroup
-constexpr int kCmpThreads = 128 * kCmpWG;         // 512
-constexpr int kBwdThreads = kCmpThreads + 128;    // + a warpgroup of TMA warp, two MMA warps and an idle warp
-// 640 threads start with 96 registers each; that pool is all the block ever has (asking for more would block a
-// warpgroup for ever): 4 * 128 * 104 + 128 * 64 = 640 * 96.
-constexpr uint32_t kComputeRegs = 104, kProducerRegs = 64;
-static_assert(kCmpThreads * kComputeRegs + 128 * kProducerRegs <= kBwdThreads * 96, "register pool");
-// The dK/dV kernel has a sixth warpgroup that only writes the finished accumulators out, so that the compute
-// warps go straight on to the next item: 768 threads start with 80 registers each.
-constexpr int kDkdvThreads = kBwdThreads + 128;
-constexpr int kEpiWarp0 = 4 * kCmpWG + 4;
-constexpr uint32_t kDkdvComputeRegs = 88, kDkdvProducerRegs = 64, kDkdvEpilogueRegs = 64;
-static_assert(kCmpThreads * kDkdvComputeRegs + 128 * kDkdvProducerRegs + 128 * kDkdvEpilogueRegs <= kDkdvThreads * 80,
-              "register pool");
-constexpr int kLoadWarpB = 4 * kCmpWG;
-constexpr int kMmaWarpB = 4 * kCmpWG + 1;
-static_assert(kCols == 32, "one 32-column tensor-memory load per operand and warp");
-
-// P and dS of kN columns for one thread. `s`/`dp` hold the raw accumulators; the results are packed 16-bit.
-// lse2 / delta are per column (kPerColumn, read from shared memory) or per thread. kMasked is a template
-// parameter so that the common fully-visible tile carries no per-element compare/select at all.
-template <int kN, bool kBf16, bool kSoftcap, bool kPerColumn, bool kMasked, bool kNeedP>
-__device__ __forceinline__ void softmax_backward_cols(const uint32_t* s, const uint32_t* dp, const float* lse2_col,
-                                                      const float* delta_col, float lse2_row, float delta_row,
-                                                      float scale_log2, float softcap_pre, int lo, int hi,
-                                                      uint32_t* pk_p, uint32_t* pk_ds) {
-#pragma unroll
-  for (int c = 0; c < kN; c += 2) {
-    float pv[2], dsv[2];
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int col = c + e;
-      float x = __uint_as_float(s[col]);
-      float dt = 1.f;
-      if (kSoftcap) {
-        x = ptx::tanh_fast(x * softcap_pre);
-        dt = 1.f - x * x;
-      }
-      const float l2 = kPerColumn ? lse2_col[col] : lse2_row;
-      const float dl = kPerColumn ? delta_col[col] : delta_row;
-      float pr = ptx::ex2(fmaf(x, scale_log2, -l2));
-      float d = pr * (__uint_as_float(dp[col]) - dl);
-      if (kSoftcap) d *= dt;
-      if (kMasked && (col < lo || col >= hi)) {
-        pr = 0.f;
-        d = 0.f;
-      }
-      pv[e] = pr;
-      dsv[e] = d;
-    }
-    if (kNeedP) pk_p[c / 2] = ptx::pack2<kBf16>(pv[0], pv[1]);
-    pk_ds[c / 2] = ptx::pack2<kBf16>(dsv[0], dsv[1]);
-  }
-}
-
 // ------------------------------------------------------------------------------------------------------------
 // 2. dK / dV
 // ------------------------------------------------------------------------------------------------------------
-struct KvItem {
-  int b, hk, kh, k0, k1, n, row0, bcoord;
-  bool valid;
-};
-
-__device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
-  // (sample, KV head)-major: the CTAs running at the same time stream the Q / dO tiles of a few heads, which then
-  // stay in L2. Inside a head: clean key tiles first, early ones first (they are seen by the most queries), then
-  // the noisy key tiles (one block of queries each) as filler.
-  KvItem it;
-  const int per_bh = 2 * p.tiles_per_half;
-  int bh, rem;
-  two_phase_order(idx, per_bh, p.n_long_kv, p.batch * p.heads_k, bh, rem);
-  it.kh = rem < p.tiles_per_half ? 1 : 0;
-  const int kt = rem < p.tiles_per_half ? rem : rem - p.tiles_per_half;
-  it.b = bh / p.heads_k;
-  it.hk = bh - it.b * p.heads_k;
-  const Sample sm = sample_of(p, it.b);
-  it.n = sm.n;
-  it.row0 = sm.row0;
-  it.bcoord = sm.bcoord;
-  it.k0 = kt * kTile;
-  it.valid = it.k0 < it.n;
-  it.k1 = imin(it.k0 + kTile, it.n);
-  return it;
-}
-
-// Query spans of the item's key tile: [0] for query tiles of the same half, [1] for noisy query tiles seeing
-// clean keys. Built once per item; classifying a query tile is then compares only.
-struct KvSpans {
-  Span same, cross;
-  bool partial_keys;
-  __device__ __forceinline__ int classify(int qh, int kh, int qa, int qb) const {
-    int c = (qh == kh ? same : cross).classify(qa, qb - qa);
-    if (c == kTileFull && partial_keys) c = kTileMasked;
-    return c;
-  }
-};
-
-__device__ __forceinline__ KvSpans make_kv_spans(const KvItem& it, int bs) {
-  KvSpans sp;
-  sp.same = query_span(it.kh, it.kh, it.k0, it.k1, it.n, bs);
-  sp.cross = it.kh == 1 ? query_span(0, 1, it.k0, it.k1, it.n, bs) : Span{0, 0, 0, 0};
-  sp.partial_keys = (it.k1 - it.k0) < kTile;
-  return sp;
-}
-
-// The query side streams in sub-tiles of kSub = 64 rows so that S^T / dP^T (64 columns each) can be double
-// buffered in tensor memory next to the dK / dV accumulators: while the compute warps turn buffer u into
-// P^T / dS^T, the tensor pipe runs dV / dK of the previous sub-tile and S^T / dP^T of the next one.
-constexpr int kSub = 64;
-constexpr int kSubCols = kSub / kCmpWG;  // 16 query columns per compute warpgroup
 
 template <int kHeadDim, int kStages>
 struct DkdvCfg {
@@ -374,11 +128,6 @@ struct DkdvCfg {
 };
 
 // Sub-steps of one item: query heads of the group x visible 128-row query tiles x two 64-row halves; a half
-// with no visible row is skipped. All roles walk this sequence identically.
-struct SubStep {
-  int h, qh, sa, sb, cls;
-};
-
 template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
 __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_constant__ BwdParams p) {
   using Cfg = DkdvCfg<kHeadDim, kStages>;
@@ -403,14 +152,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  FDA_CTA_STAMP(0, 0);
-#ifdef FDA_CLOCKRATE
-  long long cr_c0 = 0; unsigned long long cr_t0 = 0;
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    cr_c0 = clock64();
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(cr_t0));
-  }
-#endif
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kCmpWG + 2 + 4);   // compute warps, two MMA issuers, four epilogue warps
@@ -543,20 +284,14 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
           volatile int* hdr = reinterpret_cast<volatile int*>(base + Cfg::kHeaderOffset);
           hdr[0] = (last ? 1 : 0) | (st.cls == kTileMasked ? 2 : 0) | (st.qh == it.kh ? 4 : 0);
           hdr[1] = st.sa;
-#if FDA_ABL >= 3
-          ptx::mbar_expect_tx(&st_full[stage], 512);
-#else
           ptx::mbar_expect_tx(&st_full[stage], 2 * Cfg::kSubTileBytes + 512);
-#endif
           const int q_row = it.row0 + st.qh * it.n + st.sa;
-#if FDA_ABL < 3
 #pragma unroll
           for (int c = 0; c < T::kPanels; ++c) {
             ptx::tma_load_4d(base + c * Cfg::kSubPanelBytes, &p.tm_q64, &st_full[stage], c * 64, q_row, st.h, it.bcoord);
             ptx::tma_load_4d(base + Cfg::kSubTileBytes + c * Cfg::kSubPanelBytes, &p.tm_do64, &st_full[stage], c * 64,
                              q_row, st.h, it.bcoord);
           }
-#endif
           const int64_t seg = stat_segment(p, it.b, st.h, st.qh) + st.sa;
           ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes, p.lse2_pad + seg, 256, &st_full[stage]);
           ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes + 256, p.delta_pad + seg, 256, &st_full[stage]);
@@ -603,7 +338,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
           if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 52)) { alive = false; break; }
           last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
           if (!ptx::mbar_wait(&buf_free[u], ((g >> 1) & 1u) ^ 1u, abort_flag, 54)) { alive = false; break; }
-          FDA_TRACE_AT(3, g);
           ptx::tc_fence_after();
           const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
           const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
@@ -615,7 +349,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
             ptx::umma_ss_f16_lh(tmem + u * 128 + 64, v_lo + a_off, st_lo_k + do_off + b_off, kHi, idesc_s, kk > 0);
           }
           ptx::umma_commit(&sdp_full[u]);
-          FDA_TRACE_AT(4, g);
         }
         // K and V are read by these products only: the next item's tiles may load while the last dV / dK products
         // and the epilogue of this item still run
@@ -649,9 +382,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
           // the tiles themselves are read by the MMAs, after P^T / dS^T (pds_full) which follow S^T / dP^T
           if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 55)) { alive = false; break; }
           last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
-          FDA_TRACE_AT(0, g);
           if (!ptx::mbar_wait(&pds_full[u], (g >> 1) & 1u, abort_flag, 53)) { alive = false; break; }
-          FDA_TRACE_AT(1, g);
           ptx::tc_fence_after();
           const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
           const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
@@ -668,7 +399,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
           acc = true;
           ptx::umma_commit(&buf_free[u]);
           ptx::umma_commit(&st_empty[stage]);
-          FDA_TRACE_AT(2, g);
         }
         if (!alive) break;
         ptx::umma_commit(acc_full);
@@ -685,10 +415,8 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
     uint32_t n_item = 0, gc = 0;
     bool alive = true;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
-      if (threadIdx.x == 0) FDA_TRACE_KI(2, n_item);
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
       if (idx < 0 || idx >= total_items) break;
-      if (threadIdx.x == 0) FDA_TRACE_KI(3, n_item);
       const KvItem it = decode_kv_item(p, idx / Cfg::kPasses);
       const int pass_col0 = (idx % Cfg::kPasses) * Cfg::kAccDim;
       if (!it.valid) continue;
@@ -697,7 +425,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
       int same_lo, same_hi, cross_lo, cross_hi;
       query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
       query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
-      if (threadIdx.x == 0) FDA_TRACE_KI(4, n_item);
       for (bool last = false; alive && !last;) {
         const uint32_t u = gc & 1u, stage = gc % kStages;
         const uint8_t* stage_base = sStage + stage * Cfg::kStageBytes;
@@ -722,72 +449,41 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
             dlr[4 * i] = b.x; dlr[4 * i + 1] = b.y; dlr[4 * i + 2] = b.z; dlr[4 * i + 3] = b.w;
           }
         }
-        if (threadIdx.x == 0) FDA_TRACE_AT(5, gc);
         if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) { alive = false; break; }
-        if (threadIdx.x == 0) FDA_TRACE_AT(6, gc);
-        if (threadIdx.x == 0) FDA_TRACE_KC(0, gc);
         ++gc;
         ptx::tc_fence_after();
         const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
         const uint32_t dpt_t = st_t + 64;
         uint32_t sv[kSubCols], dpv[kSubCols];
-#if FDA_ABL < 2
         ptx::tmem_ld16(st_t, sv);
         ptx::tmem_ld16(dpt_t, dpv);
         ptx::tmem_wait_ld();
-#else
-        for (int i = 0; i < kSubCols; ++i) { sv[i] = i; dpv[i] = i; }
-#endif
-        if (threadIdx.x == 0) FDA_TRACE_KC(1, gc - 1);
         uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
         const float* l2 = l2r;
         const float* dl = dlr;
-#if FDA_ABL >= 1
-        for (int i = 0; i < kSubCols / 2; ++i) { pk_p[i] = sv[i]; pk_ds[i] = dpv[i]; }
-        if (false) {
-#else
         if (hdr.x & 2) {
-#endif
           const int lo = ((hdr.x & 4) ? same_lo : cross_lo) - (hdr.y + wg * kSubCols);
           const int hi = ((hdr.x & 4) ? same_hi : cross_hi) - (hdr.y + wg * kSubCols);
           softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, true, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
                                                                               p.softcap_pre, lo, hi, pk_p, pk_ds);
         } else {
-#if FDA_ABL < 1
           softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, false, true>(sv, dpv, l2, dl, 0.f, 0.f, p.scale_log2,
                                                                                p.softcap_pre, 0, 0, pk_p, pk_ds);
-#endif
         }
         // a warp overwrites only columns it has itself already loaded: its packed P^T / dS^T pieces go to the
         // start of its own kSubCols columns
-        if (threadIdx.x == 0) FDA_TRACE_KC(2, gc - 1);
-#if FDA_ABL < 2
         ptx::tmem_st8(st_t, pk_p);
         ptx::tmem_st8(dpt_t, pk_ds);
         ptx::tmem_wait_st();
-#endif
         ptx::tc_fence_before();
-        if (threadIdx.x == 0) FDA_TRACE_KC(3, gc - 1);
         ptx::mbar_arrive_warp(&pds_full[u]);
-        if (threadIdx.x == 0) FDA_TRACE_KC(4, gc - 1);
-        if (threadIdx.x == 0) FDA_TRACE_AT(7, gc - 1);
       }
       if (!alive) break;
       ++n_item;
-      if (threadIdx.x == 0) FDA_TRACE_KI(5, n_item - 1);
     }
   }
   ptx::tc_fence_before();
   __syncthreads();
-#ifdef FDA_CLOCKRATE
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    g_fda_clockrate[0] = clock64() - cr_c0;
-    g_fda_clockrate[1] = t1 - cr_t0;
-  }
-#endif
-  FDA_CTA_STAMP(0, 1);
   if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
 }
 
@@ -884,7 +580,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  FDA_CTA_STAMP(1, 0);
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kCmpWG + 2);
@@ -929,12 +624,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         const KeyPlan plan = make_key_plan(it.qh, it.qa, it.qb, it.n, bs, Cfg::kKeys);
         const QSpans spans = make_q_spans(it, bs);
         if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 71)) break;
-        FDA_TRACE_QI(6, n_item);
         ptx::mbar_expect_tx(q_full, 2 * T::kTileBytes);
         const int q_row = it.row0 + it.qh * it.n + it.qa;
         load_tile<kHeadDim>(sQ, &p.tm_q, q_full, q_row, it.h, it.bcoord);
         load_tile<kHeadDim>(sdO, &p.tm_do, q_full, q_row, it.h, it.bcoord);
-        FDA_TRACE_QI(7, n_item);
         for (int s = 0; s < plan.steps() && alive; ++s) {
           int kh, kt;
           plan.step(s, kh, kt);
@@ -989,14 +682,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           active += spans.classify(kh, kt * Cfg::kKeys, Cfg::kKeys) != kTileSkip;
         }
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 81)) break;
-        FDA_TRACE_QI(4, n_item);
         ++n_item;
         for (int j = 0; j < active; ++j, ++step) {
           const uint32_t ks = Cfg::k_slot(step), vs = Cfg::v_slot(step);
           if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 83)) { alive = false; break; }
           if (!ptx::mbar_wait(&kv_full[vs], Cfg::v_parity(step), abort_flag, 84)) { alive = false; break; }
           if (!ptx::mbar_wait(sdp_free, (step & 1) ^ 1, abort_flag, 82)) { alive = false; break; }
-          FDA_TRACE_Q(3, step);
           ptx::tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
@@ -1009,7 +700,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           }
           ptx::umma_commit(sdp_full);
           ptx::umma_commit(&kv_empty[vs]);  // V tile no longer needed
-          FDA_TRACE_Q(4, step);
         }
         // Q and dO are read by these products only: the tiles of the next item may load while the last dQ
         // product and the epilogue of this one still run
@@ -1042,9 +732,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           const uint32_t ks = Cfg::k_slot(step);
           // the K tile arrived long ago (S of this step used it); this wait only orders our reads after the copy
           if (!ptx::mbar_wait(&kv_full[ks], Cfg::k_parity(step), abort_flag, 86)) { alive = false; break; }
-          FDA_TRACE_Q(0, step);
           if (!ptx::mbar_wait(ds_full, step & 1, abort_flag, 85)) { alive = false; break; }
-          FDA_TRACE_Q(1, step);
           ptx::tc_fence_after();
           // dQ += dS K: the packed dS pieces of the compute warpgroups lie side by side, 8 columns per 16 keys
 #pragma unroll
@@ -1055,11 +743,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           }
           ptx::umma_commit(&kv_empty[ks]);
           ptx::umma_commit(ds_free);
-          FDA_TRACE_Q(2, step);
         }
         if (!alive) break;
         ptx::umma_commit(dq_full);
-        FDA_TRACE_QI(5, n_sched);
       }
     }
   }
@@ -1109,7 +795,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
 
     // One item: its steps, then the next item's record, then the epilogue. Returns whether `nxt` holds an item.
     auto run_item = [&](const ItemState& cur, ItemState& nxt) -> bool {
-      if (threadIdx.x == 0) FDA_TRACE_QI(3, n_item);
       for (int s = 0; s < cur.plan.steps() && alive; ++s) {
         int kh, kt;
         cur.plan.step(s, kh, kt);
@@ -1124,9 +809,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           lo -= kt * Cfg::kKeys + wg * kKc;
           hi -= kt * Cfg::kKeys + wg * kKc;
         }
-        if (threadIdx.x == 0) FDA_TRACE_Q(5, cnt);
         if (!ptx::mbar_wait(sdp_full, cnt & 1, abort_flag, 91)) { alive = false; break; }
-        if (threadIdx.x == 0) FDA_TRACE_Q(6, cnt);
         ptx::tc_fence_after();
         uint32_t sv[kKc], dpv[kKc];
         if (kKc == 32) {
@@ -1155,13 +838,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(ds_full);
-        if (threadIdx.x == 0) FDA_TRACE_Q(7, cnt - 1);
       }
       if (!alive) return false;
       const bool have_next = fetch(nxt);
-      if (threadIdx.x == 0) FDA_TRACE_QI(2, n_item);
       if (!ptx::mbar_wait(dq_full, n_item & 1, abort_flag, 93)) { alive = false; return false; }
-      if (threadIdx.x == 0) FDA_TRACE_QI(0, n_item);
       ++n_item;
       ptx::tc_fence_after();
       constexpr int kChunks = kHeadDim / 32;  // 32-column chunks, dealt round-robin to the warpgroups
@@ -1175,7 +855,6 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
           ptx::store_rows32_grouped<kBf16>(cur.dst, p.dq_rs, cur.rows_valid, gidx * 32, acc, p.softmax_scale, p.head_dim);
         }
       }
-      if (threadIdx.x == 0) FDA_TRACE_QI(1, n_item - 1);
       ptx::tc_fence_before();
       return have_next;
     };
@@ -1190,19 +869,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   }
   ptx::tc_fence_before();
   __syncthreads();
-  FDA_CTA_STAMP(1, 1);
   if (warp == kLoadWarpB) ptx::tmem_dealloc(tmem, 512);
-}
-
-template <typename Kernel>
-int set_smem(Kernel kernel, int bytes, bool* done) {
-  int dev = 0;
-  FDA_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 16 && !done[dev]) {
-    FDA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    done[dev] = true;
-  }
-  return FDA_OK;
 }
 
 template <int kHeadDim, int kStagesKv, int kStagesQ, bool kBf16, bool kSoftcap>
@@ -1210,8 +877,8 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
   if (stages & 2u) {
     using Cfg = DkdvCfg<kHeadDim, kStagesKv>;
     auto kernel = bwd_dkdv_kernel<kHeadDim, kStagesKv, kBf16, kSoftcap>;
-    static bool done[16] = {false};
-    int rc = set_smem(kernel, Cfg::kSmemBytes, done);
+    static PerDeviceFlags smem_set;
+    int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
     const int items = p.tiles_per_half * 2 * p.heads_k * p.batch * Cfg::kPasses;
     const int grid = items < sm_count ? items : sm_count;
@@ -1221,8 +888,8 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
   if (stages & 4u) {
     using Cfg = DqCfg<kHeadDim, kStagesQ>;
     auto kernel = bwd_dq_kernel<kHeadDim, kStagesQ, kBf16, kSoftcap>;
-    static bool done[16] = {false};
-    int rc = set_smem(kernel, Cfg::kSmemBytes, done);
+    static PerDeviceFlags smem_set;
+    int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
     const int items = p.tiles_per_half * 2 * p.heads * p.batch;
     const int grid = items < sm_count ? items : sm_count;
@@ -1246,11 +913,28 @@ inline int64_t round_up64(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
 }  // namespace
 
-// Workspace: delta_pad then lse2_pad, each batch * heads * 2 * n_pad floats (256-byte aligned pieces).
-size_t bwd_workspace_bytes(const FdaProblem& pr) {
+// bwd_fused_sm100.cu
+size_t bwd_fused_acc_bytes(const FdaProblem& pr);
+int64_t bwd_fused_acc_tiles(const FdaProblem& pr);
+int launch_bwd_fused(const BwdParams& p, int d_round, bool bf16, bool softcap, int sm_count, unsigned stages,
+                     cudaStream_t stream);
+
+// The single-pass backward adds dQ partials in an order that depends on scheduling and needs head dim <= 128.
+bool bwd_single_pass(const FdaProblem& pr) { return pr.deterministic == 0 && pr.head_dim <= 128; }
+
+// Scratch of the split backward: delta_pad then lse2_pad, each batch * heads * 2 * n_pad floats (256-byte aligned
+// pieces), then 256 bytes of work counters.
+size_t bwd_split_workspace_bytes(const FdaProblem& pr) {
   const int64_t n_pad = round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile);
   const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * n_pad * 4, 256);
   return static_cast<size_t>(2 * one + 256);
+}
+
+// The single-pass backward keeps its fp32 dQ accumulator behind that.
+size_t bwd_workspace_bytes(const FdaProblem& pr) {
+  size_t bytes = bwd_split_workspace_bytes(pr);
+  if (bwd_single_pass(pr)) bytes += static_cast<size_t>(round_up64(static_cast<int64_t>(bwd_fused_acc_bytes(pr)), 256));
+  return bytes;
 }
 
 int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
@@ -1347,6 +1031,12 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   p.lse2_pad = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + one);
   p.ticket_kv = reinterpret_cast<int*>(static_cast<uint8_t*>(a.workspace) + 2 * one);
   p.ticket_q = p.ticket_kv + 32;
+  const bool single_pass = bwd_single_pass(pr) && (stage_mask & FDA_BWD_FORCE_SPLIT) == 0;
+  if (single_pass) {
+    if (a.workspace_bytes < bwd_workspace_bytes(pr)) return FDA_ERR_WORKSPACE;
+    p.dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + 2 * one + 256);
+    p.acc_tiles = static_cast<int>(bwd_fused_acc_tiles(pr));
+  }
   if (stage_mask & 6u) FDA_CUDA_TRY(cudaMemsetAsync(p.ticket_kv, 0, 256, stream));
   const bool softcap = pr.softcap > 0.f;
   p.softmax_scale = pr.softmax_scale;
@@ -1376,43 +1066,37 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
     }
     FDA_CUDA_TRY(cudaGetLastError());
   }
+  if (single_pass) return launch_bwd_fused(p, d_round, bf16, softcap, sm_count, stage_mask, stream);
   if (d_round == 64) return dispatch_bwd<64, 6, 7>(p, sm_count, bf16, softcap, stage_mask, stream);
   if (d_round == 128) return dispatch_bwd<128, 4, 5>(p, sm_count, bf16, softcap, stage_mask, stream);
   return dispatch_bwd<256, 1, 3>(p, sm_count, bf16, softcap, stage_mask, stream);
 }
 
-#ifdef FDA_WAIT_CLOCKS
-extern "C" int fda_debug_waits_bwd(unsigned long long* out256) {
-  static unsigned long long zero[256];
-  if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;
-  if (cudaMemcpyToSymbol(g_fda_wait, zero, sizeof(zero)) != cudaSuccess) return 1;
-  return 0;
-}
-#endif
 
 // ------------------------------------------------------------------------------------------------------------
-// Backward without a caller-provided workspace (fda_bwd_noalloc). The scratch the three kernels share (delta,
-// LSE * log2(e), the two work counters) lives in this fixed array, which every GPU that loads the library holds
-// until the process exits. In host code the array's name is only a stand-in for the symbol: the device address
-// is looked up once per device, with that device current, and that pointer is what the kernels receive.
+// Backward without a caller-provided workspace (fda_bwd_noalloc). It always runs the split backward, whose
+// scratch (delta, LSE * log2(e), the two work counters) is small; that scratch lives in this fixed array, which
+// every GPU that loads the library holds until the process exits. In host code the array's name is only a
+// stand-in for the symbol: the device address is looked up once per device, with that device current, and that
+// pointer is what the kernels receive.
 // ------------------------------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_bwd_noalloc_scratch[FDA_NOALLOC_SCRATCH_BYTES];
 
 int launch_bwd_noalloc(const FdaBwdArgs& a, cudaStream_t stream) {
-  if (bwd_workspace_bytes(a.p) > static_cast<size_t>(FDA_NOALLOC_SCRATCH_BYTES)) return FDA_ERR_SCRATCH_LIMIT;
-  static void* scratch_of_device[64] = {nullptr};
+  if (bwd_split_workspace_bytes(a.p) > static_cast<size_t>(FDA_NOALLOC_SCRATCH_BYTES)) return FDA_ERR_SCRATCH_LIMIT;
+  static std::atomic<void*> scratch_of_device[kMaxCachedDevices];
   int dev = 0;
   FDA_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return FDA_ERR_UNSUPPORTED;
-  if (scratch_of_device[dev] == nullptr) {
-    void* ptr = nullptr;
+  const bool cached = dev >= 0 && dev < kMaxCachedDevices;
+  void* ptr = cached ? scratch_of_device[dev].load(std::memory_order_acquire) : nullptr;
+  if (ptr == nullptr) {
     FDA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_bwd_noalloc_scratch));
-    scratch_of_device[dev] = ptr;
+    if (cached) scratch_of_device[dev].store(ptr, std::memory_order_release);
   }
   FdaBwdArgs with_scratch = a;
-  with_scratch.workspace = scratch_of_device[dev];
+  with_scratch.workspace = ptr;
   with_scratch.workspace_bytes = FDA_NOALLOC_SCRATCH_BYTES;
-  return launch_bwd(with_scratch, stream, 7u);
+  return launch_bwd(with_scratch, stream, 7u | FDA_BWD_FORCE_SPLIT);
 }
 
 int read_status_bwd(int32_t* out4) {

@@ -26,42 +26,6 @@
 #include "ptx.cuh"
 #include "sched.cuh"
 
-#ifdef FDA_CTA_TIMES
-__device__ unsigned long long g_fda_cta_times[2 * 160];
-extern "C" int fda_debug_cta_times_fwd(unsigned long long* out) {
-  return cudaMemcpyFromSymbol(out, g_fda_cta_times, sizeof(unsigned long long) * 320) == cudaSuccess ? 0 : 1;
-}
-#endif
-#ifdef FDA_TRACE
-__device__ long long g_fda_trace_f[8 * 256];
-extern "C" int fda_debug_trace_fwd(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_fda_trace_f, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : 1;
-}
-#define FDA_TRACE_PUTF(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace_f[(row) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define FDA_TRACE_PUTF(row, idx) do { } while (0)
-#endif
-// FDA_TRACE=9: steps of the forward kernel; FDA_TRACE=8: its item boundaries
-#if defined(FDA_TRACE) && FDA_TRACE == 9
-#define FDA_TRACE_F(row, idx) FDA_TRACE_PUTF(row, idx)
-#else
-#define FDA_TRACE_F(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 8
-#define FDA_TRACE_FI(row, idx) FDA_TRACE_PUTF(row, idx)
-#else
-#define FDA_TRACE_FI(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 6   // the four warps of softmax warpgroup 0, step by step
-#define FDA_TRACE_FW(row, idx) FDA_TRACE_PUTF(row, idx)
-#else
-#define FDA_TRACE_FW(row, idx) do { } while (0)
-#endif
-#if defined(FDA_TRACE) && FDA_TRACE == 7   // inside the epilogue
-#define FDA_TRACE_FE(row, idx) FDA_TRACE_PUTF(row, idx)
-#else
-#define FDA_TRACE_FE(row, idx) do { } while (0)
-#endif
 
 #ifndef FDA_SHORT8_FWD
 #define FDA_SHORT8_FWD 2   // eighths of a (sample, head)'s items that count as short
@@ -70,21 +34,12 @@ extern "C" int fda_debug_trace_fwd(long long* out) {
 namespace fda {
 namespace {
 
-#ifdef FDA_PHASE_CLOCKS
-// Debug build only: cycles one softmax thread spends per phase, summed over CTAs (wait, load, math, store,
-// epilogue/other) and the number of tile steps.
-__device__ unsigned long long g_fda_phase[16];
-#endif
 
 constexpr int kBlockM = 128;  // query rows per tile (= tensor-memory lanes)
 constexpr int kBlockN = 128;  // keys per tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
-#ifndef FDA_MUFU_LOCK
-#define FDA_MUFU_LOCK 0
-#endif
-constexpr bool kUseMufuLock = FDA_MUFU_LOCK != 0;  // turn-taking of the two softmax warpgroups (experiment)
 
 struct FwdParams {
   CUtensorMap tm_q, tm_k, tm_v;
@@ -238,24 +193,15 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kQTiles);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
-  int* mufu_lock = reinterpret_cast<int*>(mbox + 1);  // one per warp quadrant (= SM sub-partition)
   ItemDesc* desc = reinterpret_cast<ItemDesc*>(reinterpret_cast<uint8_t*>(bars) + 512);  // two slots
   static_assert(2 * sizeof(ItemDesc) <= 512, "item descriptions");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef FDA_CTA_TIMES
-  if (threadIdx.x == 0 && blockIdx.x < 160) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_fda_cta_times[blockIdx.x] = t;
-  }
-#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kQTiles + 1);
-    for (int i = 0; i < 4; ++i) mufu_lock[i] = 0;
     ptx::mbar_init(q_full, 1);
     ptx::mbar_init(q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
@@ -336,7 +282,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             if (s == 0 && which == 0) {
               // Q after the first K tile: the first MMA needs both, the previous item may still own Q.
               if (!ptx::mbar_wait(q_empty, (n_item & 1) ^ 1, abort_flag, 12)) { alive = false; break; }
-              FDA_TRACE_FI(0, n_item);
               ptx::mbar_expect_tx(q_full, ntiles * Cfg::kTileBytes);
               for (int t = 0; t < ntiles; ++t) {
 #pragma unroll
@@ -394,7 +339,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_peek(mbox, n_sched, abort_flag);
         if (idx < 0 || idx >= p.total_items) break;
-        FDA_TRACE_FI(2, n_item);
         const Item it = desc[n_sched & 1u].it;
         const KeyPlan plan = desc[n_sched & 1u].plan;
         TileSpans spans[kQTiles];
@@ -403,9 +347,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         sched_release<false>(mbox, n_sched);
         if (!it.valid) continue;
         const int steps = plan.steps();
-        FDA_TRACE_FI(3, n_item);
         if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 21)) { alive = false; break; }
-        FDA_TRACE_FI(4, n_item);
         bool pend[kQTiles], o_acc[kQTiles];
 #pragma unroll
         for (int t = 0; t < kQTiles; ++t) { pend[t] = false; o_acc[t] = false; }
@@ -425,7 +367,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           for (int t = 0; t < kQTiles; ++t) {
             if (pend[t]) {
               if (!ptx::mbar_wait(&p_full[t], cnt_p[t] & 1, abort_flag, 24)) { alive = false; break; }
-              FDA_TRACE_F(2 * t, cnt_p[t]);
               ++cnt_p[t];
               ptx::tc_fence_after();
               issue_pv(t, slot_v % kStages, o_acc[t]);
@@ -435,7 +376,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             if (s < steps && spans[t].classify(kh, kt) != kTileSkip) {
               issue_s(t, slot_k % kStages);
               ptx::umma_commit(&s_full[t]);
-              FDA_TRACE_F(2 * t + 1, cnt_p[t]);
               pend[t] = true;
             }
           }
@@ -452,7 +392,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         for (int t = 0; t < kQTiles; ++t) {
           if (it.qa + t * kBlockM < it.qb) ptx::umma_commit(&o_full[t]);
         }
-        FDA_TRACE_FI(1, n_item);
         slot += 2 * steps;
         ++n_item;
       }
@@ -470,17 +409,8 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
     uint32_t cnt_s = 0, cnt_o = 0;
     bool alive = true;
     uint8_t* stage_o = sStageO + t * Cfg::kStageOBytes;
-#ifdef FDA_PHASE_CLOCKS
-    long long ph_wait = 0, ph_ld = 0, ph_math = 0, ph_st = 0, ph_epi = 0, ph_steps = 0, ph_t = 0, ph_owait = 0, ph_pre = 0, ph_sched = 0, ph_setup = 0;
-#define FDA_PH(acc) do { const long long _n = clock64(); acc += _n - ph_t; ph_t = _n; } while (0)
-    ph_t = clock64();
-#else
-#define FDA_PH(acc) do {} while (0)
-#endif
     for (uint32_t n_sched = 0; alive; ++n_sched) {
-      FDA_PH(ph_pre);
       const int idx = sched_peek(mbox, n_sched, abort_flag);
-      FDA_PH(ph_sched);
       if (idx < 0 || idx >= p.total_items) break;
       const Item it = desc[n_sched & 1u].it;
       const TileSpans spans = desc[n_sched & 1u].spans[t];
@@ -518,18 +448,12 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       float m_run = -INFINITY;  // reference maximum (unscaled scores, or tanh values with softcap)
       float l_run = 0.f;
       bool o_started = false;
-      FDA_PH(ph_setup);
-      if (threadIdx.x == 0) FDA_TRACE_FI(7, cnt_o);
       for (int s = 0; s < steps && alive; ++s) {
         int kh, kt;
         plan.step(s, kh, kt);
         const int cls = spans.classify(kh, kt);
         if (cls == kTileSkip) continue;
-        FDA_PH(ph_pre);
         if (!ptx::mbar_wait(&s_full[t], cnt_s & 1, abort_flag, 31)) { alive = false; break; }
-        if (row == 0) FDA_TRACE_F(4 + 2 * t, cnt_s);
-        if (t == 0 && lane == 0) FDA_TRACE_FW(4 + quad, cnt_s);
-        FDA_PH(ph_wait);
         ++cnt_s;
         ptx::tc_fence_after();
         float v[kBlockN];
@@ -538,19 +462,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 #pragma unroll
           for (int c = 0; c < kBlockN / 32; ++c) ptx::tmem_ld32(tmem_s + c * 32, u + c * 32);
           ptx::tmem_wait_ld();
-        }
-        FDA_PH(ph_ld);
-        // The two warps that share an SM sub-partition (same quadrant, one per query tile) take turns in the
-        // exp-heavy part: whoever gets its S first runs at full MUFU rate and hands its P to the MMA warp early,
-        // so the tensor pipe works on one tile while the other tile is in its softmax. Only a scheduling hint:
-        // nothing is protected by the lock, and a warp that cannot get it in time goes ahead without it.
-        bool have_lock = false;
-        if (kQTiles > 1 && kUseMufuLock) {
-          if (lane == 0) {
-            int spins = 0;
-            while (!(have_lock = (atomicCAS(&mufu_lock[quad], 0, 1) == 0)) && ++spins < 20000) {}
-          }
-          have_lock = __shfl_sync(0xffffffffu, have_lock ? 1 : 0, 0) != 0;
         }
         if (kSoftcap) {
 #pragma unroll
@@ -623,35 +534,20 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           }
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        if (kQTiles > 1 && kUseMufuLock) {
-          __syncwarp();
-          if (lane == 0 && have_lock) atomicExch(&mufu_lock[quad], 0);
-        }
-        FDA_PH(ph_math);
 #pragma unroll
         for (int c = 0; c < Cfg::kPCols / 32; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&p_full[t]);
-        if (row == 0) FDA_TRACE_F(5 + 2 * t, cnt_s - 1);
-        if (t == 0 && lane == 0) FDA_TRACE_FW(quad, cnt_s - 1);
         o_started = true;
-        FDA_PH(ph_st);
-#ifdef FDA_PHASE_CLOCKS
-        ++ph_steps;
-#endif
       }
       if (!alive) break;
       // ---- epilogue: O / l -> global, LSE
-      FDA_PH(ph_pre);
       if (!ptx::mbar_wait(&o_full[t], cnt_o & 1, abort_flag, 32)) { alive = false; break; }
-      if (threadIdx.x == 0) FDA_TRACE_FI(5, cnt_o);
-      FDA_PH(ph_owait);
       ++cnt_o;
       ptx::tc_fence_after();
       const float inv_l = out_scale / l_run;
       const int64_t srow = static_cast<int64_t>(it.row0) + it.qh * it.n + r;
-      if (threadIdx.x == 0) FDA_TRACE_FE(0, cnt_o - 1);
       bool lse_done = false;
       auto store_lse = [&]() {
         lse_done = true;
@@ -677,7 +573,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             ptx::tmem_ld32(tmem_o + pass * 64, o);
             ptx::tmem_ld32(tmem_o + pass * 64 + 32, o + 32);
             ptx::tmem_wait_ld();
-            if (threadIdx.x == 0) FDA_TRACE_FE(1 + 3 * pass, cnt_o - 1);
             uint32_t w[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
@@ -686,7 +581,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             // the previous copy out of this warp's buffer (last pass or last item) must have read it completely
             if (lane == 0) ptx::bulk_wait_group_read0();
             __syncwarp();
-            if (threadIdx.x == 0) FDA_TRACE_FE(2 + 3 * pass, cnt_o - 1);
             ptx::st_shared_row128_sw(my_stage, lane, w);
             ptx::fence_proxy_async_smem();
             __syncwarp();
@@ -694,7 +588,6 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
               ptx::tma_store_4d(&p.tm_o, my_stage, pass * 64, it.row0 + it.qh * it.n + ta + quad * 32, it.h, it.bcoord);
               ptx::bulk_commit_group();
             }
-            if (threadIdx.x == 0) FDA_TRACE_FE(3 + 3 * pass, cnt_o - 1);
             // the log-sum-exp goes out while the tile copy reads the buffer
             if (!lse_done) store_lse();
           }
@@ -721,52 +614,23 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       }
       if (!lse_done) store_lse();
       ptx::tc_fence_before();
-      if (threadIdx.x == 0) FDA_TRACE_FE(7, cnt_o - 1);
-      FDA_PH(ph_epi);
-      if (threadIdx.x == 0) FDA_TRACE_FI(6, cnt_o - 1);
     }
     // shared memory must outlive the tile copies that read it
     if (lane == 0) ptx::bulk_wait_group0();
-#ifdef FDA_PHASE_CLOCKS
-    if (threadIdx.x == 0) {
-      atomicAdd(&g_fda_phase[8], (unsigned long long)ph_sched);
-      atomicAdd(&g_fda_phase[9], (unsigned long long)ph_setup);
-      atomicAdd(&g_fda_phase[6], (unsigned long long)ph_owait);
-      atomicAdd(&g_fda_phase[7], (unsigned long long)ph_pre);
-      atomicAdd(&g_fda_phase[0], (unsigned long long)ph_wait);
-      atomicAdd(&g_fda_phase[1], (unsigned long long)ph_ld);
-      atomicAdd(&g_fda_phase[2], (unsigned long long)ph_math);
-      atomicAdd(&g_fda_phase[3], (unsigned long long)ph_st);
-      atomicAdd(&g_fda_phase[4], (unsigned long long)ph_epi);
-      atomicAdd(&g_fda_phase[5], (unsigned long long)ph_steps);
-    }
-#endif
   }
 
   ptx::tc_fence_before();
   __syncthreads();
-#ifdef FDA_CTA_TIMES
-  if (threadIdx.x == 0 && blockIdx.x < 160) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_fda_cta_times[160 + blockIdx.x] = t;
-  }
-#endif
   if (warp == Cfg::kLoadWarp) ptx::tmem_dealloc(tmem, 512);
 }
-#undef FDA_PH
 
 template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
 int launch_fwd_instance(const FwdParams& p, int grid, cudaStream_t stream) {
   using Cfg = FwdConfig<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
   auto kernel = fwd_kernel<kHeadDim, kQTiles, kStages, kType, kSoftcap>;
-  static bool attr_set[16] = {false};
-  int dev = 0;
-  FDA_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 16 && !attr_set[dev]) {
-    FDA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set[dev] = true;
-  }
+  static PerDeviceFlags smem_set;
+  const int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
+  if (rc) return rc;
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
   FDA_CUDA_TRY(cudaGetLastError());
   return FDA_OK;
@@ -888,23 +752,7 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   return dispatch_fwd<256, 1, 2>(p, grid, bf16, softcap, stream);
 }
 
-#ifdef FDA_PHASE_CLOCKS
-extern "C" int fda_debug_phase_clocks(unsigned long long* out8) {
-  unsigned long long zero[16] = {0};
-  if (cudaMemcpyFromSymbol(out8, g_fda_phase, sizeof(zero)) != cudaSuccess) return 1;
-  if (cudaMemcpyToSymbol(g_fda_phase, zero, sizeof(zero)) != cudaSuccess) return 1;
-  return 0;
-}
-#endif
 
-#ifdef FDA_WAIT_CLOCKS
-extern "C" int fda_debug_waits_fwd(unsigned long long* out256) {
-  static unsigned long long zero[256];
-  if (cudaMemcpyFromSymbol(out256, g_fda_wait, sizeof(zero)) != cudaSuccess) return 1;
-  if (cudaMemcpyToSymbol(g_fda_wait, zero, sizeof(zero)) != cudaSuccess) return 1;
-  return 0;
-}
-#endif
 
 int read_status_fwd(int32_t* out4) {
   int zero[4] = {0, 0, 0, 0};

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -79,6 +80,27 @@ inline int encode_tile_map(CUtensorMap* map, const void* ptr, int elem_bytes, bo
   return FDA_OK;
 }
 
+// Per-device caches are indexed by the CUDA device ordinal up to this limit; beyond it nothing is cached (every call
+// does the full work), so no ordinal is ever refused or silently skipped. A cudaDeviceReset() clears the function
+// attributes the flags stand for: a process that resets a device must not call the library on it afterwards.
+constexpr int kMaxCachedDevices = 64;
+
+struct PerDeviceFlags {
+  std::atomic<bool> done[kMaxCachedDevices];
+};
+
+// Raise a kernel's dynamic shared-memory limit once per device (the attribute is per device and per function).
+template <typename Kernel>
+int set_dynamic_smem(Kernel kernel, int bytes, PerDeviceFlags& flags) {
+  int dev = 0;
+  FDA_CUDA_TRY(cudaGetDevice(&dev));
+  const bool cached = dev >= 0 && dev < kMaxCachedDevices;
+  if (cached && flags.done[dev].load(std::memory_order_acquire)) return FDA_OK;
+  FDA_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (cached) flags.done[dev].store(true, std::memory_order_release);
+  return FDA_OK;
+}
+
 struct DeviceInfo {
   int device = -1;
   int sm_count = 0;
@@ -86,10 +108,11 @@ struct DeviceInfo {
 };
 
 inline int current_device_info(DeviceInfo* out) {
-  static thread_local DeviceInfo cache[16];
+  static thread_local DeviceInfo cache[kMaxCachedDevices];
   int dev = 0;
   FDA_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 16 && cache[dev].device == dev) {
+  const bool cached = dev >= 0 && dev < kMaxCachedDevices;
+  if (cached && cache[dev].device == dev) {
     *out = cache[dev];
     return FDA_OK;
   }
@@ -97,7 +120,7 @@ inline int current_device_info(DeviceInfo* out) {
   d.device = dev;
   FDA_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
   FDA_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
-  if (dev >= 0 && dev < 16) cache[dev] = d;
+  if (cached) cache[dev] = d;
   *out = d;
   return FDA_OK;
 }
@@ -109,6 +132,7 @@ int launch_bwd_noalloc(const FdaBwdArgs& a, cudaStream_t stream);
 int launch_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, cudaStream_t stream);
 int read_status_fwd(int32_t* out4);
 int read_status_bwd(int32_t* out4);
+int read_status_bwd_fused(int32_t* out4);
 int read_status_selftest(int32_t* out4);
 
 }  // namespace fda

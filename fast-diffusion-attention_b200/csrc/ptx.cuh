@@ -73,7 +73,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // returns at once so the CTA can drain, free its tensor memory and exit. Returns false when aborted.
 constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds at the boost clock
 
-__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
@@ -81,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, v
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 127u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = code;
         if (atomicCAS(&g_fda_status[0], 0, code) == 0) {
           g_fda_status[1] = static_cast<int>(blockIdx.x);
@@ -95,26 +96,6 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, v
   return true;
 }
 
-#ifdef FDA_WAIT_CLOCKS
-}  // namespace ptx
-// Debug build only: cycles spent inside each wait site (indexed by its code) and the number of waits, recorded by
-// lane 0 of the first compute warp and of the producer / MMA warps.
-static __device__ unsigned long long g_fda_wait[256];
-namespace ptx {
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  const long long t0 = clock64();
-  const bool ok = mbar_wait_impl(bar, parity, abort_flag, code);
-  if ((threadIdx.x & 31) == 0 && (threadIdx.x == 0 || threadIdx.x + 64 >= blockDim.x)) {
-    atomicAdd(&g_fda_wait[code & 127], static_cast<unsigned long long>(clock64() - t0));
-    atomicAdd(&g_fda_wait[128 + (code & 127)], 1ull);
-  }
-  return ok;
-}
-#else
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  return mbar_wait_impl(bar, parity, abort_flag, code);
-}
-#endif
 
 // ---- TMA tile loads (no cluster fan-out: every CTA fetches its own tiles) ----------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {

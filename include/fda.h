@@ -108,10 +108,18 @@ size_t fda_bwd_workspace_bytes(const FdaProblem* p);
 int fda_fwd(const FdaFwdArgs* args, void* stream);
 int fda_bwd(const FdaBwdArgs* args, void* stream);
 
-/* Same as fda_bwd but runs only the stages selected by `stage_mask`, in order, on `stream`: bit 0 the
- * preprocess (delta and LSE*log2e into the workspace), bit 1 the dK/dV kernel, bit 2 the dQ kernel. Later
- * stages read what the preprocess left in the workspace. For profiling and per-kernel timing; the reference
- * has the same stages as separate launches (csrc/fda/flash_bwd_launch_template.h:47-239). */
+/* Same as fda_bwd but runs only the stages selected by `stage_mask`, in order, on `stream`. Later stages read
+ * what earlier ones left in the workspace. For profiling and per-kernel timing; the reference has the same
+ * stages as separate launches (csrc/fda/flash_bwd_launch_template.h:47-239).
+ * The backward has two forms. The single-pass form (deterministic == 0 and head_dim <= 128) computes dK, dV and
+ * the partial dQ of every (key tile, query tile) pair in one kernel and adds the partials into an fp32
+ * accumulator in the workspace; the order of those adds varies from run to run. The split form (everything
+ * else, or FDA_BWD_FORCE_SPLIT) runs a dK/dV kernel and a dQ kernel with no cross-block reduction; its result
+ * is bitwise reproducible. */
+#define FDA_BWD_STAGE_PREPROCESS 1u /* delta = rowsum(dO * O) and LSE * log2(e) into the workspace */
+#define FDA_BWD_STAGE_MAIN 2u       /* single-pass kernel (with its accumulator zero-fill), or the dK/dV kernel */
+#define FDA_BWD_STAGE_DQ 4u         /* accumulator -> dQ conversion, or the dQ kernel */
+#define FDA_BWD_FORCE_SPLIT 8u      /* use the split form even where the single-pass form applies */
 int fda_bwd_stages(const FdaBwdArgs* args, unsigned stage_mask, void* stream);
 
 /* Backward pass for callers that cannot hand the library a workspace. Some hosts of this library own no device
@@ -119,11 +127,13 @@ int fda_bwd_stages(const FdaBwdArgs* args, unsigned stage_mask, void* stream);
  * forbids allocator calls on its request path, a host language binding that reaches CUDA only through this ABI,
  * or a training loop that runs under a memory plan fixed ahead of time. For them fda_bwd is unusable because it
  * needs fda_bwd_workspace_bytes() of caller-provided scratch. This entry point takes the same arguments but
- * ignores args->workspace / args->workspace_bytes: the per-row statistics and the two work counters live in a
- * fixed array of FDA_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU that loads it (it is
- * held until the process exits). The caller still provides every input and output tensor.
- *  - Problems whose scratch need exceeds the array (batch * heads * round_up(n, 128) * 16 bytes + 512) are
- *    rejected with FDA_ERR_SCRATCH_LIMIT; nothing is launched.
+ * ignores args->workspace / args->workspace_bytes. It always runs the split form of the backward (see
+ * fda_bwd_stages), whose scratch is small: the per-row statistics and the two work counters, kept in a fixed
+ * array of FDA_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU that loads it (it is held
+ * until the process exits). The caller still provides every input and output tensor; the result is bitwise the
+ * one fda_bwd gives with deterministic = 1.
+ *  - The scratch need is what fda_bwd_workspace_bytes() returns for the same problem with deterministic = 1.
+ *    Problems that need more than the array holds are rejected with FDA_ERR_SCRATCH_LIMIT; nothing is launched.
  *  - It never calls cudaMalloc / cudaFree or any allocating routine. The first call on a device looks up the
  *    device address of the array (cudaGetSymbolAddress) with that device current; make that first call outside
  *    of any stream capture.
@@ -158,8 +168,10 @@ int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int
 
 /* ---- tensor-core self test (GPU): C[128 x n] = A[128 x k] * B with the operand layouts the kernels use ---- */
 /* mode 0: A, B both K-major from shared memory; mode 1: A from tensor memory, B MN-major from shared memory;
- * a, b, c are device pointers: a (128, k) bf16 row-major; b (n, k) bf16 row-major for mode 0, (k, n) row-major
- * for mode 1; c (128, n) float32. k and n are multiples of 64, at most 128 (k) / 256 (n). */
+ * mode 2: A and B both MN-major from shared memory (the dQ^T product of the single-pass backward).
+ * a, b, c are device pointers: a (128, k) bf16 row-major, for mode 2 its transpose (k, 128) row-major; b (n, k)
+ * bf16 row-major for mode 0, (k, n) row-major for modes 1 and 2; c (128, n) float32. k and n are multiples of 64,
+ * at most 128 (k) / 256 (n). */
 int fda_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, void* stream);
 
 #ifdef __cplusplus

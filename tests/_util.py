@@ -38,3 +38,15 @@ def assert_within_2x(name, got, truth, plain, rtol=2.0, atol=None):
     assert err <= rtol * err_plain + atol, (
         f"{name}: max error {err:.3e} > {rtol} * {err_plain:.3e} (plain PyTorch) + {atol:.1e}")
     return err, err_plain
+
+
+def assert_same_gradients(name, got, want, exact):
+    """Bitwise equality, or (dq of the single-pass backward, whose fp32 partial sums are added in an order that
+    depends on scheduling) equality up to one rounding step of the 16-bit result."""
+    if exact:
+        assert torch.equal(got, want), f"{name} differs"
+        return
+    a, b = got.float(), want.float()
+    tol = torch.maximum(a.abs(), b.abs()) * 2.0 ** -6 + 1e-6
+    bad = (a - b).abs() > tol
+    assert not bad.any(), f"{name}: {int(bad.sum())} elements differ by more than one rounding step"

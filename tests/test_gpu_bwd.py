@@ -6,7 +6,7 @@ plain = the oracle evaluated in the input precision. Also: bitwise reproducibili
 import pytest
 import torch
 
-from _util import assert_within_2x
+from _util import assert_same_gradients, assert_within_2x
 from fast_diffusion_attention import _lib, diffusion_attn_func, diffusion_attn_varlen_func
 from oracle import diffusion_oracle as orc
 
@@ -110,8 +110,9 @@ def test_backward_bitwise_reproducible(heads, heads_k, deterministic):
 
     ref = run()
     for _ in range(4):
-        for x, y in zip(run(), ref):
-            assert torch.equal(x, y)
+        for name, x, y in zip(("dq", "dk", "dv"), run(), ref):
+            # without `deterministic` dq comes from global fp32 adds in scheduling order (one rounding step of slack)
+            assert_same_gradients(name, x, y, exact=deterministic or name != "dq")
 
 
 def test_backward_matches_golden_fixture():

@@ -125,5 +125,6 @@ def test_compiles_as_one_graph_and_matches_eager():
 
     want = run(step)
     got = run(torch.compile(step, fullgraph=True, backend="aot_eager"))
-    for a, b in zip(got, want):
-        assert torch.equal(a, b)
+    from _util import assert_same_gradients
+    for name, a, b in zip(("dq", "dk", "dv"), got, want):
+        assert_same_gradients(name, a, b, exact=name != "dq")   # dq: global fp32 adds in scheduling order
