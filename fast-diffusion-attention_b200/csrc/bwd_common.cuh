@@ -48,6 +48,7 @@ struct BwdParams {
   int* ticket_q;
   float* dq_acc;     // single-pass backward: fp32 dQ accumulator, [heads][acc_tiles][head dim][64 queries]
   int acc_tiles;     // 64-row accumulator tiles per query head
+  int64_t acc_floats;   // size of the accumulator
   int wide_store;      // dq/dk/dv rows allow 32-byte stores
   float scale_log2, softcap_pre, softmax_scale;
 };

@@ -1,16 +1,19 @@
 // Single-pass backward of block-diffusion attention for sm_100a: dK, dV and dQ from five GEMMs per tile pair.
 //
-// One CTA per (128-key tile, KV head, sample, half), persistent. K and V stay in shared memory; the visible query
-// rows of every query head of the group stream through in sub-tiles of 64 rows. Per sub-tile:
-//   S^T = K Q^T, dP^T = V dO^T          (keys on tensor-memory lanes, 64 columns each, double buffered)
-//   P^T = exp2(S^T c - LSE2), dS^T = P^T (dP^T - delta)          (compute warps; P^T back to tensor memory,
-//                                                                 dS^T to shared memory, both 16-bit)
-//   dV += P^T dO, dK += dS^T Q          (accumulators in tensor memory for the whole key tile)
-//   dQ^T = K^T dS^T                     (head dim on lanes, 64 query columns, written over the consumed dP^T buffer)
-// The partial dQ^T of a (key tile, query sub-tile) pair is added into an fp32 accumulator in global memory with
-// vector reductions (red.global.add.v4.f32); `bwd_dq_convert_kernel` then scales, rounds and transposes it into dQ.
-// The accumulator is private scratch, so its layout is chosen for the adds: one 64-query sub-tile is stored as
-// [head dim][64 queries], which is the tensor-memory layout of dQ^T (a thread owns one head-dim row).
+// One CTA per (128-key tile, KV head, sample, half), persistent. K and V stay in shared memory; the visible
+// 128-row query tiles of every query head of the group stream through. Per (key tile, query tile) step:
+//   S^T  = K Q^T                        keys on tensor-memory lanes, 128 query columns
+//   P^T  = exp2(S^T c - LSE2)           compute warps; written back over S^T as 16-bit
+//   dP^T = V dO^T                       a second 128-column buffer
+//   dS^T = P^T (dP^T - delta)           compute warps; to shared memory as 16-bit, [keys][queries]
+//   dV  += P^T dO, dK += dS^T Q         accumulators in tensor memory for the whole key tile
+//   dQ^T = K^T dS^T                     head dim on lanes, 128 query columns, written over the consumed dP^T buffer
+// The two halves of the arithmetic hang on different products, so they overlap different MMAs: P^T is computed while
+// dP^T (and the tail of the previous step) runs, dS^T while dV runs. The partial dQ^T of a step is added into an fp32
+// accumulator in global memory (red.global.add.f32, one 128-byte line per warp instruction);
+// `bwd_dq_convert_kernel` then scales and rounds it into dQ. The accumulator holds rows of queries ([rows][head dim]
+// per query head): a thread of the drain warps owns one head-dim row of dQ^T, so a warp adds 32 consecutive floats
+// of one query row per instruction.
 //
 // The reference does the same five GEMMs per pair with an fp32 dQ accumulator reduced through global memory
 // (csrc/fda/mainloop_bwd_sm90_tma_gmma_ws.hpp:815-984 `bwd_step`, :605-664 `store_dq`, there with
@@ -19,83 +22,148 @@
 // backward keeps the two-kernel split (dK/dV kernel + dQ kernel), which has no cross-CTA reduction.
 #include "bwd_common.cuh"
 
+#ifdef FDA_TRACE
+__device__ long long g_fda_trace[16 * 256];
+extern "C" int fda_debug_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_fda_trace, sizeof(long long) * 16 * 256) == cudaSuccess ? 0 : 1;
+}
+#define FDA_TRACE_PUT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define FDA_TRACE_PUT(row, idx) do { } while (0)
+#endif
+
 namespace fda {
 namespace {
 
-template <int kHeadDim, int kStages>
+template <int kHeadDim, int kSlots, int kDoSlots>
 struct FusedCfg {
   using T = TileCfg<kHeadDim>;
-  static constexpr int kSubTileBytes = kSub * kHeadDim * 2;     // Q or dO sub-tile
-  static constexpr int kSubPanelBytes = kSub * 128;             // one 64-column panel of a sub-tile
-  static constexpr int kStageBytes = 2 * kSubTileBytes + 1024;  // Q, dO, lse2[64], delta[64], header
-  static constexpr int kHeaderOffset = 2 * kSubTileBytes + 512;
-  static constexpr int kDsBytes = kTile * kSub * 2;             // dS^T: [128 keys][64 queries], 128-byte rows
-  static constexpr int kSmemBytes = 2 * T::kTileBytes + kStages * kStageBytes + 2 * kDsBytes + 1024 + 512;
-  // tensor memory: buffer u holds S^T at u*128 (P^T written back in place) and dP^T at u*128 + 64 (dQ^T of the
-  // same sub-step lands there once dP^T is in registers); dK and dV behind
-  static constexpr int kTmemDK = 256, kTmemDV = 256 + kHeadDim;
-  static_assert(kHeadDim == 64 || kHeadDim == 128, "the fused backward covers head dimensions up to 128");
-  static_assert(kStageBytes % 1024 == 0 && kDsBytes % 1024 == 0, "tiles stay 1024-byte aligned for the swizzle");
+  static constexpr int kDsPanelBytes = kTile * 128;          // [128 keys][64 queries] 16-bit
+  static constexpr int kDsBytes = 2 * kDsPanelBytes;         // dS^T: two 64-query panels
+  static constexpr int kStatBytes = 2 * kTile * 4;           // lse2[128], delta[128] of a query tile
+  static constexpr int kOffQ = 2 * T::kTileBytes;            // K, V first (V directly behind K)
+  static constexpr int kOffDo = kOffQ + kSlots * T::kTileBytes;
+  static constexpr int kOffDs = kOffDo + kDoSlots * T::kTileBytes;
+  static constexpr int kStageChunk = 32 * 32 * 4;            // one warp's 32 head-dim rows x 32 query columns of dQ^T
+  static constexpr int kOffStage = kOffDs + kDsBytes;        // [4 warps][2 slots][kStageChunk]
+  static constexpr int kOffStat = kOffStage + 4 * 2 * kStageChunk;
+  static constexpr int kOffBar = kOffStat + kSlots * kStatBytes;
+  static constexpr int kSmemBytes = kOffBar + 512;
+  // tensor memory: S^T / P^T at 0, dP^T / dQ^T at 128, dK and dV behind
+  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
+  static_assert(kHeadDim == 64 || kHeadDim == 128, "the single-pass backward covers head dimensions up to 128");
+  static_assert(kOffStat % 1024 == 0, "tiles stay 1024-byte aligned for the swizzle");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
+  static_assert((12 + 2 * kSlots + 2 * kDoSlots) * 8 + 8 + 16 + 16 * kSlots <= 384, "barrier area");
 };
 
-// Index of the 64-row accumulator tile that holds query row `sa` (a multiple of 64) of half `qh` of a sample whose
-// first row in the packed row space is `grow0`. Every half starts at its own tile: the "+ 2 b + qh" gives each of
-// the 2 * batch halves one tile of slack, so rounding the start down never lets two halves share a tile.
-__device__ __forceinline__ int acc_tile_of(int grow0, int n, int b, int qh, int sa) {
-  return (grow0 + qh * n) / kSub + 2 * b + qh + sa / kSub;
+// 768 threads start with 80 registers each. The compute warps hold a step's 32 probabilities per thread across the
+// two halves of the arithmetic; the producer warpgroup and the drain / epilogue warpgroup get by with less.
+constexpr uint32_t kFusedComputeRegs = 88, kFusedProducerRegs = 64, kFusedDrainRegs = 64;
+static_assert(kCmpThreads * kFusedComputeRegs + 128 * kFusedProducerRegs + 128 * kFusedDrainRegs <= kDkdvThreads * 80,
+              "register pool");
+
+// Rows of the dQ accumulator come in blocks of 64. Every half of every sample starts at its own block: the
+// "+ 2 b + qh" gives each of the 2 * batch halves one block of slack, so rounding the start down never lets two
+// halves share a block. Returns the first accumulator row of query row `qa` (a multiple of 64) of half `qh` of a
+// sample whose first row in the packed row space is `grow0`.
+__device__ __forceinline__ int acc_row_of(int grow0, int n, int b, int qh, int qa) {
+  return ((grow0 + qh * n) / 64 + 2 * b + qh) * 64 + qa;
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(__uint_as_float(a)),
-               "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d))
-               : "memory");
+// One step of an item: a visible 128-row query tile of one query head.
+struct QStep {
+  int h, qh, qa, cls;
+};
+
+template <typename Fn>
+__device__ __forceinline__ bool for_each_qstep(const KvItem& it, const QueryPlan& plan, const KvSpans& spans, int group,
+                                               Fn&& fn) {
+  for (int g = 0; g < group; ++g) {
+    for (int s = 0; s < plan.steps(); ++s) {
+      QStep st;
+      int qt;
+      plan.step(s, it.kh, st.qh, qt);
+      st.qa = qt * kTile;
+      const int qb = imin(st.qa + kTile, it.n);
+      st.cls = spans.classify(st.qh, it.kh, st.qa, qb);
+      if (st.cls == kTileSkip) continue;
+      st.h = it.hk * group + g;
+      if (!fn(st)) return false;
+    }
+  }
+  return true;
 }
 
-template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
+template <int kHeadDim, int kSlots, int kDoSlots, bool kBf16, bool kSoftcap>
 __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid_constant__ BwdParams p) {
-  using Cfg = FusedCfg<kHeadDim, kStages>;
+  using Cfg = FusedCfg<kHeadDim, kSlots, kDoSlots>;
   using T = TileCfg<kHeadDim>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The tiles need 1024-byte alignment for the 128-byte swizzle. Dynamic shared memory starts at the beginning of the
+  // block's window, which is aligned that far; the budget leaves no room to round the base up, so a base that is not
+  // aligned is reported through the status word instead.
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = smem + T::kTileBytes;   // directly behind K: for head dim 64 it is the second panel of the M = 128
                                         // operand of dQ^T (rows 64..127 of that product are never read)
-  uint8_t* sStage = smem + 2 * T::kTileBytes;
-  uint8_t* sDs = sStage + kStages * Cfg::kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDs + 2 * Cfg::kDsBytes);
+  uint8_t* sQ = smem + Cfg::kOffQ;
+  uint8_t* sDo = smem + Cfg::kOffDo;
+  uint8_t* sDs = smem + Cfg::kOffDs;
+  uint8_t* sStage = smem + Cfg::kOffStage;
+  uint8_t* sStat = smem + Cfg::kOffStat;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   uint64_t* kv_full = bars;
   uint64_t* kv_empty = bars + 1;
-  uint64_t* st_full = bars + 2;
-  uint64_t* st_empty = st_full + kStages;
-  uint64_t* sdp_full = st_empty + kStages;   // [2] S^T / dP^T of buffer u are complete
-  uint64_t* pds_full = sdp_full + 2;         // [2] P^T (tensor memory) and dS^T (shared memory) are written
-  uint64_t* dq_full = pds_full + 2;          // [2] dQ^T of buffer u is complete
-  uint64_t* buf_free = dq_full + 2;          // [2] dV / dK have read buffer u and dQ^T is in the drain warps' registers
-  uint64_t* acc_full = buf_free + 2;
+  uint64_t* q_full = bars + 2;                 // [kSlots] Q tile, its statistics and the step header
+  uint64_t* q_empty = q_full + kSlots;
+  uint64_t* do_full = q_empty + kSlots;        // [kDoSlots] dO tile
+  uint64_t* do_empty = do_full + kDoSlots;
+  uint64_t* s_full = do_empty + kDoSlots;      // S^T complete
+  uint64_t* dp_full = s_full + 1;              // dP^T complete
+  uint64_t* p_full = dp_full + 1;              // P^T written over S^T
+  uint64_t* ds_full = p_full + 1;              // dS^T in shared memory, dP^T in registers
+  uint64_t* s_free = ds_full + 1;              // dV has read P^T: the next S^T may overwrite it
+  uint64_t* dq_full = s_free + 1;              // dQ^T complete
+  uint64_t* dp_free = dq_full + 1;             // dQ^T is in the drain warps' registers: the next dP^T may overwrite it
+  uint64_t* ds_free = dp_free + 1;             // dQ^T and dK have read dS^T: the next step may overwrite it
+  uint64_t* acc_full = ds_free + 1;
   uint64_t* acc_free = acc_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* dq_desc = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2][2]: {last sub-step, accumulator tile}
-  SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
-  static_assert((12 + 2 * kStages) * 8 + 6 * 4 <= 256, "barrier area");
+  volatile int* dq_desc = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [2][2]: {flags, first accumulator row}
+  volatile int* hdr = reinterpret_cast<volatile int*>(tmem_slot + 6);       // [kSlots][4]
+  SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 384);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((ptx::smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && atomicCAS(&g_fda_status[0], 0, 120) == 0) {
+      g_fda_status[1] = static_cast<int>(blockIdx.x);
+      g_fda_status[2] = 0;
+      g_fda_status[3] = static_cast<int>(ptx::smem_u32(smem) & 1023u);
+    }
+    return;
+  }
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     sched_init(mbox, 4 * kCmpWG + 2 + 4);   // compute warps, two MMA issuers, four drain / epilogue warps
     ptx::mbar_init(kv_full, 1);
     ptx::mbar_init(kv_empty, 1);
-    for (int i = 0; i < kStages; ++i) {
-      ptx::mbar_init(&st_full[i], 1);
-      ptx::mbar_init(&st_empty[i], 1);
+    for (int i = 0; i < kSlots; ++i) {
+      ptx::mbar_init(&q_full[i], 1);
+      ptx::mbar_init(&q_empty[i], 1);
     }
-    for (int u = 0; u < 2; ++u) {
-      ptx::mbar_init(&sdp_full[u], 1);
-      ptx::mbar_init(&pds_full[u], 4 * kCmpWG);
-      ptx::mbar_init(&dq_full[u], 1);
-      ptx::mbar_init(&buf_free[u], 1 + 4);   // the commit behind dV / dK and the four drain warps
+    for (int i = 0; i < kDoSlots; ++i) {
+      ptx::mbar_init(&do_full[i], 1);
+      ptx::mbar_init(&do_empty[i], 2);   // dP^T (issuer 1) and dV (issuer 2) have both read the tile
     }
+    ptx::mbar_init(s_full, 1);
+    ptx::mbar_init(dp_full, 1);
+    ptx::mbar_init(p_full, 4 * kCmpWG);
+    ptx::mbar_init(ds_full, 4 * kCmpWG);
+    ptx::mbar_init(s_free, 1);
+    ptx::mbar_init(dq_full, 1);
+    ptx::mbar_init(dp_free, 4);
+    ptx::mbar_init(ds_free, 1);
     ptx::mbar_init(acc_full, 1);
     ptx::mbar_init(acc_free, 4);
     ptx::fence_mbar_init();
@@ -114,14 +182,14 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
 
   if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------------------------- dQ drain + dK/dV epilogue
-    // Four warps, one per quarter of the tensor-memory lanes. Per sub-step they add the partial dQ^T (lane = head-dim
-    // row, 64 query columns) into the global accumulator; after the last sub-step of an item they write dK and dV.
-    ptx::reg_release_to<kDkdvEpilogueRegs>();
+    // Four warps, one per quarter of the tensor-memory lanes. Per step they add the partial dQ^T (lane = head-dim
+    // row, 128 query columns) into the global accumulator; after the last step of an item they write dK and dV.
+    ptx::reg_release_to<kFusedDrainRegs>();
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const bool drain_rows = quad * 32 < kHeadDim;   // head dim 64: the upper two quarters hold nothing of dQ^T
-    uint32_t n_item = 0, gd = 0;
+    uint32_t n_item = 0, gd = 0, n_bulk = 0;
     bool alive = true;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
       const int idx = sched_consume<true>(mbox, n_sched, abort_flag);
@@ -129,34 +197,61 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
       const KvItem it = decode_kv_item(p, idx);
       if (!it.valid) continue;
       for (bool last = false; alive && !last; ++gd) {
-        const uint32_t u = gd & 1u, par = (gd >> 1) & 1u;
-        // the compute warps' barrier orders their description of the sub-step before our read of it
-        if (!ptx::mbar_wait(&pds_full[u], par, abort_flag, 63)) { alive = false; break; }
-        last = dq_desc[2 * u] != 0;
-        const int tile = dq_desc[2 * u + 1];
-        if (!ptx::mbar_wait(&dq_full[u], par, abort_flag, 64)) { alive = false; break; }
+        const uint32_t par = gd & 1u;
+        // the compute warps' barrier orders their description of the step before our read of it
+        if (!ptx::mbar_wait(ds_full, par, abort_flag, 63)) { alive = false; break; }
+        const int flags = dq_desc[2 * par];
+        const int acc_row = dq_desc[2 * par + 1];
+        last = (flags & 1) != 0;
+        const int rows_left = flags >> 8;   // query rows of this tile that exist (1..128)
+        if (!ptx::mbar_wait(dq_full, par, abort_flag, 64)) { alive = false; break; }
         ptx::tc_fence_after();
-        float* dst = p.dq_acc + static_cast<size_t>(tile) * (kSub * kHeadDim) + row * kSub;
-        const bool row_used = row < p.head_dim;
+        if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(11, gd);
+        // Blocks of 32 query rows of the accumulator are stored as [head dim / 32][32 queries][32 head-dim values]: a
+        // warp's 32 x 32 piece of dQ^T goes through shared memory (a thread writes its head-dim value of each query,
+        // 32 lanes = 128 consecutive bytes) and out as ONE 4 KB bulk reduction, issued by lane 0. Two staging slots per
+        // warp alternate, so tensor memory is read out at shared-memory speed and the adds drain in the background.
+        float* dst = p.dq_acc + static_cast<size_t>(acc_row) * kHeadDim + quad * 1024;
         if (drain_rows) {
-          uint32_t a[32];
-          ptx::tmem_ld32(tmem + u * 128 + 64 + lane_addr, a);
-          ptx::tmem_wait_ld();
-          if (row_used) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t a[32];
+            ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + c * 32, a);
+            float* stage = reinterpret_cast<float*>(sStage + (quad * 2 + (n_bulk & 1u)) * Cfg::kStageChunk);
+            // the bulk reduction that last read this slot (two chunks ago) must have finished reading it
+            if (lane == 0) ptx::bulk_wait_group_read<1>();
+            __syncwarp();
+            ptx::tmem_wait_ld();
+            if (c == 3) {
+              ptx::tc_fence_before();
+              ptx::mbar_arrive_warp(dp_free);
+              if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(12, gd);
+            }
+            if (c * 32 < rows_left) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) red_add_v4(dst + 4 * i, a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
-          }
-          ptx::tmem_ld32(tmem + u * 128 + 64 + lane_addr + 32, a);
-          ptx::tmem_wait_ld();
-          ptx::tc_fence_before();
-          ptx::mbar_arrive_warp(&buf_free[u]);
-          if (row_used) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) red_add_v4(dst + 32 + 4 * i, a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+              for (int i = 0; i < 32; ++i) stage[i * 32 + lane] = __uint_as_float(a[i]);
+              ptx::fence_async_smem();
+              __syncwarp();
+#ifndef FDA_NORED
+              if (lane == 0) {
+                float* target = dst + c * (32 * kHeadDim);
+                if (target >= p.dq_acc && target + 1024 <= p.dq_acc + p.acc_floats) {
+                  ptx::bulk_reduce_add_f32(target, stage, Cfg::kStageChunk);
+                  ptx::bulk_commit_group();
+                } else if (atomicCAS(&g_fda_status[0], 0, 121) == 0) {   // never expected: recorded, not performed
+                  g_fda_status[1] = static_cast<int>(blockIdx.x);
+                  g_fda_status[2] = acc_row;
+                  g_fda_status[3] = flags;
+                }
+              }
+#endif
+              ++n_bulk;
+            }
           }
         } else {
-          ptx::mbar_arrive_warp(&buf_free[u]);
+          ptx::mbar_arrive_warp(dp_free);
         }
+        if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(13, gd);
       }
       if (!alive) break;
       const int kj = it.k0 + row;
@@ -186,8 +281,9 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         }
       }
     }
+    if (lane == 0) ptx::bulk_wait_group0();   // every reduction this warp issued has been performed
   } else if (warp >= 4 * kCmpWG) {
-  ptx::reg_release_to<kDkdvProducerRegs>();
+  ptx::reg_release_to<kFusedProducerRegs>();
   if (warp == kLoadWarpB) {
     // ------------------------------------------------------------------------------------------------ producer
     if (lane == 0) {
@@ -206,41 +302,40 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         const int k_row = it.row0 + it.kh * it.n + it.k0;
         load_tile<kHeadDim>(sK, &p.tm_k, kv_full, k_row, it.hk, it.bcoord);
         load_tile<kHeadDim>(sV, &p.tm_v, kv_full, k_row, it.hk, it.bcoord);
-        // The loader alone walks the item's geometry. Each stage carries a header for the other roles:
-        // {bit 0 last sub-step of the item, bit 1 partially masked, bit 2 queries of the keys' own half; first row;
-        // accumulator tile of the sub-step's dQ}. A sub-step is sent when its successor is known, so that the last
-        // one can be marked.
-        auto emit = [&](const SubStep& st, bool last) -> bool {
-          const uint32_t stage = gc % kStages;
-          if (!ptx::mbar_wait(&st_empty[stage], ((gc / kStages) & 1) ^ 1, abort_flag, 42)) return false;
-          uint8_t* base = sStage + stage * Cfg::kStageBytes;
-          volatile int* hdr = reinterpret_cast<volatile int*>(base + Cfg::kHeaderOffset);
-          hdr[0] = (last ? 1 : 0) | (st.cls == kTileMasked ? 2 : 0) | (st.qh == it.kh ? 4 : 0);
-          hdr[1] = st.sa;
-          hdr[2] = st.h * p.acc_tiles + acc_tile_of(grow0, it.n, it.b, st.qh, st.sa);
-          ptx::mbar_expect_tx(&st_full[stage], 2 * Cfg::kSubTileBytes + 512);
-          const int q_row = it.row0 + st.qh * it.n + st.sa;
-#pragma unroll
-          for (int c = 0; c < T::kPanels; ++c) {
-            ptx::tma_load_4d(base + c * Cfg::kSubPanelBytes, &p.tm_q64, &st_full[stage], c * 64, q_row, st.h, it.bcoord);
-            ptx::tma_load_4d(base + Cfg::kSubTileBytes + c * Cfg::kSubPanelBytes, &p.tm_do64, &st_full[stage], c * 64,
-                             q_row, st.h, it.bcoord);
-          }
-          const int64_t seg = stat_segment(p, it.b, st.h, st.qh) + st.sa;
-          ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes, p.lse2_pad + seg, 256, &st_full[stage]);
-          ptx::bulk_load_1d(base + 2 * Cfg::kSubTileBytes + 256, p.delta_pad + seg, 256, &st_full[stage]);
+        // The loader alone walks the item's geometry. Each step carries a header for the other roles:
+        // {bit 0 last step of the item, bit 1 partially masked, bit 2 queries of the keys' own half, bits 8.. the
+        // number of query rows that exist; first query row; first accumulator row of the step's dQ}. A step is sent
+        // when its successor is known, so that the last one can be marked.
+        auto emit = [&](const QStep& st, bool last) -> bool {
+          const uint32_t slot = gc % kSlots, par = ((gc / kSlots) & 1u) ^ 1u;
+          if (!ptx::mbar_wait(&q_empty[slot], par, abort_flag, 42)) return false;
+          volatile int* h4 = hdr + 4 * slot;
+          h4[0] = (last ? 1 : 0) | (st.cls == kTileMasked ? 2 : 0) | (st.qh == it.kh ? 4 : 0) |
+                  (imin(kTile, it.n - st.qa) << 8);
+          h4[1] = st.qa;
+          h4[2] = st.h * p.acc_tiles * 64 + acc_row_of(grow0, it.n, it.b, st.qh, st.qa);
+          ptx::mbar_expect_tx(&q_full[slot], T::kTileBytes + Cfg::kStatBytes);
+          const int q_row = it.row0 + st.qh * it.n + st.qa;
+          load_tile<kHeadDim>(sQ + slot * T::kTileBytes, &p.tm_q, &q_full[slot], q_row, st.h, it.bcoord);
+          const int64_t seg = stat_segment(p, it.b, st.h, st.qh) + st.qa;
+          ptx::bulk_load_1d(sStat + slot * Cfg::kStatBytes, p.lse2_pad + seg, kTile * 4, &q_full[slot]);
+          ptx::bulk_load_1d(sStat + slot * Cfg::kStatBytes + kTile * 4, p.delta_pad + seg, kTile * 4, &q_full[slot]);
+          const uint32_t dslot = gc % kDoSlots, dpar = ((gc / kDoSlots) & 1u) ^ 1u;
+          if (!ptx::mbar_wait(&do_empty[dslot], dpar, abort_flag, 43)) return false;
+          ptx::mbar_expect_tx(&do_full[dslot], T::kTileBytes);
+          load_tile<kHeadDim>(sDo + dslot * T::kTileBytes, &p.tm_do, &do_full[dslot], q_row, st.h, it.bcoord);
           ++gc;
           return true;
         };
-        SubStep pend{};
+        QStep pend{};
         bool have = false;
-        alive = for_each_substep(it, plan, spans, group, [&](const SubStep& st) -> bool {
+        alive = for_each_qstep(it, plan, spans, group, [&](const QStep& st) -> bool {
           if (have && !emit(pend, false)) return false;
           pend = st;
           have = true;
           return true;
         });
-        // every valid key tile is seen at least by the queries of its own rows, so there is a last sub-step
+        // every valid key tile is seen at least by the queries of its own rows, so there is a last step
         if (alive && have) alive = emit(pend, true);
         ++n_item;
       }
@@ -249,15 +344,16 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
   } else if (warp == kMmaWarpB) {
     // ------------------------------------------------------------------- MMA issuer 1: S^T = K Q^T, dP^T = V dO^T
     // Two threads issue the MMAs of this kernel, so that the barrier waits and commits of one overlap the MMAs of
-    // the other. Sub-step g may overwrite buffer g & 1 once dV / dK of sub-step g - 2 have read P^T from it and
-    // its dQ^T has been drained (buf_free).
+    // the other. S^T of step g + 1 may overwrite P^T of step g once dV has read it (s_free); dP^T of step g + 1
+    // may overwrite dQ^T of step g once the drain warps hold it (dp_free).
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
-      const uint32_t idesc_s = ptx::make_idesc(kTile, kSub, kFmt, false, false);
+      const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
       const uint32_t k_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), 16);
       const uint32_t v_lo = ptx::smem_desc_lo(ptx::smem_u32(sV), 16);
-      const uint32_t st_lo_k = ptx::smem_desc_lo(ptx::smem_u32(sStage), 16);
+      const uint32_t q_lo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16);
+      const uint32_t do_lo = ptx::smem_desc_lo(ptx::smem_u32(sDo), 16);
       uint32_t n_item = 0, g = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -267,35 +363,49 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         if (!it.valid) continue;
         if (!ptx::mbar_wait(kv_full, n_item & 1, abort_flag, 51)) break;
         for (bool last = false; alive && !last; ++g) {
-          const uint32_t u = g & 1u, stage = g % kStages;
-          if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 52)) { alive = false; break; }
-          last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
-          if (!ptx::mbar_wait(&buf_free[u], ((g >> 1) & 1u) ^ 1u, abort_flag, 54)) { alive = false; break; }
+          const uint32_t slot = g % kSlots, spar = (g / kSlots) & 1u;
+          const uint32_t t_off = slot * (T::kTileBytes >> 4);
+          if (!ptx::mbar_wait(&q_full[slot], spar, abort_flag, 52)) { alive = false; break; }
+          last = (hdr[4 * slot] & 1) != 0;
+          if (!ptx::mbar_wait(s_free, (g & 1u) ^ 1u, abort_flag, 54)) { alive = false; break; }
           ptx::tc_fence_after();
-          const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
-          const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
+          FDA_TRACE_PUT(0, g);
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-            const uint32_t a_off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
-            const uint32_t b_off = ((kk / 4) * Cfg::kSubPanelBytes + (kk % 4) * 32) >> 4;
-            ptx::umma_ss_f16_lh(tmem + u * 128, k_lo + a_off, st_lo_k + q_off + b_off, kHi, idesc_s, kk > 0);
-            ptx::umma_ss_f16_lh(tmem + u * 128 + 64, v_lo + a_off, st_lo_k + do_off + b_off, kHi, idesc_s, kk > 0);
+            const uint32_t off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemS, k_lo + off, q_lo + t_off + off, kHi, idesc_s, kk > 0);
           }
-          ptx::umma_commit(&sdp_full[u]);
+          ptx::umma_commit(s_full);
+          const uint32_t dslot = g % kDoSlots;
+          if (!ptx::mbar_wait(&do_full[dslot], (g / kDoSlots) & 1u, abort_flag, 56)) { alive = false; break; }
+          if (!ptx::mbar_wait(dp_free, (g & 1u) ^ 1u, abort_flag, 58)) { alive = false; break; }
+          ptx::tc_fence_after();
+          FDA_TRACE_PUT(1, g);
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint32_t off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDP, v_lo + off, do_lo + dslot * (T::kTileBytes >> 4) + off, kHi, idesc_s,
+                                kk > 0);
+          }
+          ptx::umma_commit(dp_full);
+          ptx::umma_commit(&do_empty[dslot]);
+          FDA_TRACE_PUT(2, g);
         }
         ++n_item;
       }
     }
   } else if (warp == kMmaWarpB + 1) {
-    // -------------------------------------------------- MMA issuer 2: dQ^T = K^T dS^T, dV += P^T dO, dK += dS^T Q
+    // -------------------------------------------------- MMA issuer 2: dV += P^T dO, dQ^T = K^T dS^T, dK += dS^T Q
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_g = ptx::make_idesc(kTile, kHeadDim, kFmt, false, true);   // A K-major, B MN-major
-      const uint32_t idesc_q = ptx::make_idesc(kTile, kSub, kFmt, true, true);        // A and B MN-major
+      const uint32_t idesc_q = ptx::make_idesc(kTile, kTile, kFmt, true, true);       // A and B MN-major
       constexpr uint32_t kHi = ptx::smem_desc_hi(1024);
-      const uint32_t st_lo_mn = ptx::smem_desc_lo(ptx::smem_u32(sStage), Cfg::kSubPanelBytes);   // Q / dO, MN-major B
-      const uint32_t kt_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), T::kPanelBytes);   // K^T: the key rows are the reduction
-      const uint32_t ds_lo = ptx::smem_desc_lo(ptx::smem_u32(sDs), 16);              // dS^T, one 64-query panel
+      const uint32_t q_mn = ptx::smem_desc_lo(ptx::smem_u32(sQ), T::kPanelBytes);     // Q / dO as MN-major B: rows of
+      const uint32_t do_mn = ptx::smem_desc_lo(ptx::smem_u32(sDo), T::kPanelBytes);   // queries are the reduction
+      const uint32_t kt_lo = ptx::smem_desc_lo(ptx::smem_u32(sK), T::kPanelBytes);    // K^T: key rows are the reduction
+      const uint32_t ds_mn = ptx::smem_desc_lo(ptx::smem_u32(sDs), Cfg::kDsPanelBytes);   // dS^T as B of dQ^T
+      const uint32_t ds_k = ptx::smem_desc_lo(ptx::smem_u32(sDs), 16);                // dS^T as K-major A of dK
       uint32_t g = 0, n_item_b = 0;
       bool alive = true;
       for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -308,34 +418,44 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         if (!ptx::mbar_wait(acc_free, (n_item_b & 1u) ^ 1u, abort_flag, 57)) break;
         ++n_item_b;
         for (bool last = false; alive && !last; ++g) {
-          const uint32_t u = g & 1u, stage = g % kStages;
-          if (!ptx::mbar_wait(&st_full[stage], (g / kStages) & 1u, abort_flag, 55)) { alive = false; break; }
-          last = (*reinterpret_cast<const volatile int*>(sStage + stage * Cfg::kStageBytes + Cfg::kHeaderOffset) & 1) != 0;
-          if (!ptx::mbar_wait(&pds_full[u], (g >> 1) & 1u, abort_flag, 53)) { alive = false; break; }
+          const uint32_t slot = g % kSlots, spar = (g / kSlots) & 1u;
+          const uint32_t t_off = slot * (T::kTileBytes >> 4);
+          if (!ptx::mbar_wait(&q_full[slot], spar, abort_flag, 55)) { alive = false; break; }
+          last = (hdr[4 * slot] & 1) != 0;
+          if (!ptx::mbar_wait(p_full, g & 1u, abort_flag, 53)) { alive = false; break; }
           ptx::tc_fence_after();
-          const uint32_t q_off = stage * (Cfg::kStageBytes >> 4);
-          const uint32_t do_off = q_off + (Cfg::kSubTileBytes >> 4);
-          const uint32_t st_t = tmem + u * 128, dq_t = tmem + u * 128 + 64;
-          const uint32_t ds_u = ds_lo + u * (Cfg::kDsBytes >> 4);
-          // dQ^T first: its drain (tensor memory -> registers -> global adds) then runs under dV / dK
+          FDA_TRACE_PUT(3, g);
+          // dV += P^T dO: P^T of the 16 queries of reduction step kk sits at column 32 (kk / 2) + 8 (kk % 2)
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
-            ptx::umma_ss_f16_lh(dq_t, kt_lo + kk * (2048 >> 4), ds_u + kk * (2048 >> 4), kHi, idesc_q, kk > 0);
+            ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, tmem + Cfg::kTmemS + 32 * (kk / 2) + 8 * (kk % 2),
+                                do_mn + (g % kDoSlots) * (T::kTileBytes >> 4) + kk * (2048 >> 4), kHi, idesc_g,
+                                (acc || kk > 0) ? 1u : 0u);
           }
-          ptx::umma_commit(&dq_full[u]);
-          // K is read by S^T (already complete for every sub-step of this item) and by dQ^T: after the last dQ^T
-          // the next item's K and V may load
+          ptx::umma_commit(s_free);
+          ptx::umma_commit(&do_empty[g % kDoSlots]);
+          FDA_TRACE_PUT(4, g);
+          if (!ptx::mbar_wait(ds_full, g & 1u, abort_flag, 59)) { alive = false; break; }
+          ptx::tc_fence_after();
+          FDA_TRACE_PUT(5, g);
+          // dQ^T before dK: its drain (tensor memory -> registers -> global adds) then runs under dK
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk) {
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDP, kt_lo + kk * (2048 >> 4), ds_mn + kk * (2048 >> 4), kHi, idesc_q, kk > 0);
+          }
+          ptx::umma_commit(dq_full);
+          // K is read by S^T (complete for every step of this item by now) and by dQ^T: after the last dQ^T the next
+          // item's K and V may load
           if (last) ptx::umma_commit(kv_empty);
 #pragma unroll
-          for (int kk = 0; kk < kSub / 16; ++kk) {
-            ptx::umma_ts_f16_lh(tmem + Cfg::kTmemDV, st_t + kk * kSubCols, st_lo_mn + do_off + kk * (2048 >> 4), kHi,
-                                idesc_g, (acc || kk > 0) ? 1u : 0u);
-            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDK, ds_u + kk * (32 >> 4), st_lo_mn + q_off + kk * (2048 >> 4), kHi,
-                                idesc_g, (acc || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kTile / 16; ++kk) {
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDK, ds_k + (((kk / 4) * Cfg::kDsPanelBytes + (kk % 4) * 32) >> 4),
+                                q_mn + t_off + kk * (2048 >> 4), kHi, idesc_g, (acc || kk > 0) ? 1u : 0u);
           }
           acc = true;
-          ptx::umma_commit(&buf_free[u]);
-          ptx::umma_commit(&st_empty[stage]);
+          ptx::umma_commit(&q_empty[slot]);
+          ptx::umma_commit(ds_free);
+          FDA_TRACE_PUT(6, g);
         }
         if (!alive) break;
         ptx::umma_commit(acc_full);
@@ -343,15 +463,18 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
     }
   }
   } else {
-    ptx::reg_acquire_to<kDkdvComputeRegs>();
+    ptx::reg_acquire_to<kFusedComputeRegs>();
     // -------------------------------------------------------------------------------------- softmax backward
-    const int wg = warp >> 2;                  // which kSubCols query columns of a sub-tile
+    const int wg = warp >> 2;                  // which 32 query columns of the step
     const int quad = warp & 3;
     const int row = quad * 32 + lane;          // key row inside the tile
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    // this thread's two 16-byte pieces of its dS^T row (128-byte swizzle: piece c of row r sits at c ^ (r & 7))
-    const uint32_t ds_off0 = row * 128 + (((2 * wg) ^ (row & 7)) << 4);
-    const uint32_t ds_off1 = row * 128 + (((2 * wg + 1) ^ (row & 7)) << 4);
+    const uint32_t s_t = tmem + Cfg::kTmemS + lane_addr + wg * kCols;
+    const uint32_t dp_t = tmem + Cfg::kTmemDP + lane_addr + wg * kCols;
+    // this thread's row of the dS^T panel that holds its 32 queries: four 16-byte pieces starting at piece 4 (wg & 1)
+    // (128-byte swizzle: piece c of row r sits at c ^ (r & 7))
+    uint8_t* ds_row = sDs + (wg >> 1) * Cfg::kDsPanelBytes + row * 128;
+    const int ds_piece0 = 4 * (wg & 1);
     uint32_t gc = 0;
     bool alive = true;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
@@ -364,63 +487,124 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
       int same_lo, same_hi, cross_lo, cross_hi;
       query_interval(it.kh, it.kh, kj, it.n, bs, same_lo, same_hi);
       query_interval(0, 1, kj, it.n, bs, cross_lo, cross_hi);
-      for (bool last = false; alive && !last;) {
-        const uint32_t u = gc & 1u, stage = gc % kStages;
-        const uint8_t* stage_base = sStage + stage * Cfg::kStageBytes;
-        const float* stats = reinterpret_cast<const float*>(stage_base + 2 * Cfg::kSubTileBytes);
-        // the stage barrier orders the header and the bulk copies of lse2 / delta before our reads
-        if (!ptx::mbar_wait(&st_full[stage], (gc / kStages) & 1u, abort_flag, 60)) { alive = false; break; }
-        int hdr0, hdr1, hdr2;
-        hdr0 = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[0];
-        hdr1 = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[1];
-        hdr2 = reinterpret_cast<const volatile int*>(stage_base + Cfg::kHeaderOffset)[2];
+      for (bool last = false; alive && !last; ++gc) {
+        const uint32_t slot = gc % kSlots, par = gc & 1u;
+        const float* stats = reinterpret_cast<const float*>(sStat + slot * Cfg::kStatBytes) + wg * kCols;
+        // the Q barrier orders the header and the bulk copies of lse2 / delta before our reads
+        if (!ptx::mbar_wait(&q_full[slot], (gc / kSlots) & 1u, abort_flag, 60)) { alive = false; break; }
+        const int hdr0 = hdr[4 * slot], hdr1 = hdr[4 * slot + 1], hdr2 = hdr[4 * slot + 2];
         last = (hdr0 & 1) != 0;
-        // the per-column statistics of this warp's 16 query columns come into registers now, as 16-byte loads, while
-        // the S^T / dP^T products are still running (scalar loads later would queue behind the MMAs' operand fetches)
-        float l2r[kSubCols], dlr[kSubCols];
-        {
-          const float4* l2v = reinterpret_cast<const float4*>(stats + wg * kSubCols);
-          const float4* dlv = reinterpret_cast<const float4*>(stats + kSub + wg * kSubCols);
+        const bool masked = (hdr0 & 2) != 0;
+        // visible query columns of this thread's key, relative to its first column of the step
+        const int lo = ((hdr0 & 4) ? same_lo : cross_lo) - (hdr1 + wg * kCols);
+        const int hi = ((hdr0 & 4) ? same_hi : cross_hi) - (hdr1 + wg * kCols);
+        if constexpr (!kSoftcap) {
+          float pr[kCols];   // the step's probabilities of this thread, kept from the first half of the arithmetic
+          if (!ptx::mbar_wait(s_full, par, abort_flag, 61)) { alive = false; break; }
+          ptx::tc_fence_after();
+          if (threadIdx.x == 0) FDA_TRACE_PUT(7, gc);
+          {
+            uint32_t sv[kCols];
+            ptx::tmem_ld16(s_t, sv);
+            ptx::tmem_ld16(s_t + 16, sv + 16);
+            ptx::tmem_wait_ld();
+            const float4* l2v = reinterpret_cast<const float4*>(stats);
+            if (!masked) {
 #pragma unroll
-          for (int i = 0; i < kSubCols / 4; ++i) {
-            const float4 a = l2v[i], b = dlv[i];
-            l2r[4 * i] = a.x; l2r[4 * i + 1] = a.y; l2r[4 * i + 2] = a.z; l2r[4 * i + 3] = a.w;
-            dlr[4 * i] = b.x; dlr[4 * i + 1] = b.y; dlr[4 * i + 2] = b.z; dlr[4 * i + 3] = b.w;
+              for (int i = 0; i < kCols / 4; ++i) {
+                const float4 l2 = l2v[i];
+                pr[4 * i] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i]), p.scale_log2, -l2.x));
+                pr[4 * i + 1] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 1]), p.scale_log2, -l2.y));
+                pr[4 * i + 2] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 2]), p.scale_log2, -l2.z));
+                pr[4 * i + 3] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 3]), p.scale_log2, -l2.w));
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < kCols / 4; ++i) {
+                const float4 l2 = l2v[i];
+                const float l2a[4] = {l2.x, l2.y, l2.z, l2.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int c = 4 * i + j;
+                  const float v = ptx::ex2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2a[j]));
+                  pr[c] = (c < lo || c >= hi) ? 0.f : v;
+                }
+              }
+            }
           }
-        }
-        if (!ptx::mbar_wait(&sdp_full[u], (gc >> 1) & 1u, abort_flag, 61)) { alive = false; break; }
-        ++gc;
-        ptx::tc_fence_after();
-        const uint32_t st_t = tmem + u * 128 + lane_addr + wg * kSubCols;
-        const uint32_t dpt_t = st_t + 64;
-        uint32_t sv[kSubCols], dpv[kSubCols];
-        ptx::tmem_ld16(st_t, sv);
-        ptx::tmem_ld16(dpt_t, dpv);
-        ptx::tmem_wait_ld();
-        uint32_t pk_p[kSubCols / 2], pk_ds[kSubCols / 2];
-        if (hdr0 & 2) {
-          const int lo = ((hdr0 & 4) ? same_lo : cross_lo) - (hdr1 + wg * kSubCols);
-          const int hi = ((hdr0 & 4) ? same_hi : cross_hi) - (hdr1 + wg * kSubCols);
-          softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, true, true>(sv, dpv, l2r, dlr, 0.f, 0.f, p.scale_log2,
-                                                                              p.softcap_pre, lo, hi, pk_p, pk_ds);
+          {
+            uint32_t pk[kCols / 2];
+#pragma unroll
+            for (int c = 0; c < kCols / 2; ++c) pk[c] = ptx::pack2<kBf16>(pr[2 * c], pr[2 * c + 1]);
+            // a warp overwrites only columns it has itself already loaded: the 16-bit P^T of its 32 queries goes to
+            // the first 16 of its own 32 columns
+            ptx::tmem_st16(s_t, pk);
+          }
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive_warp(p_full);
+          if (threadIdx.x == 0) FDA_TRACE_PUT(8, gc);
+          if (!ptx::mbar_wait(dp_full, par, abort_flag, 65)) { alive = false; break; }
+          // dQ^T and dK of the previous step have read the dS^T tile (long ago in the steady state)
+          if (!ptx::mbar_wait(ds_free, par ^ 1u, abort_flag, 66)) { alive = false; break; }
+          ptx::tc_fence_after();
+          if (threadIdx.x == 0) FDA_TRACE_PUT(9, gc);
+          {
+            uint32_t dpv[kCols];
+            ptx::tmem_ld16(dp_t, dpv);
+            ptx::tmem_ld16(dp_t + 16, dpv + 16);
+            ptx::tmem_wait_ld();
+            const float4* dlv = reinterpret_cast<const float4*>(stats + kTile);
+            // masked positions have P = 0, so dS = 0 there without another compare
+#pragma unroll
+            for (int i = 0; i < kCols / 8; ++i) {
+              const float4 d0 = dlv[2 * i], d1 = dlv[2 * i + 1];
+              const float dl[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+              uint32_t pk[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int c = 8 * i + 2 * j;
+                pk[j] = ptx::pack2<kBf16>(pr[c] * (__uint_as_float(dpv[c]) - dl[2 * j]),
+                                          pr[c + 1] * (__uint_as_float(dpv[c + 1]) - dl[2 * j + 1]));
+              }
+              ptx::st_shared_v4(ds_row + (((ds_piece0 + i) ^ (row & 7)) << 4), pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
         } else {
-          softmax_backward_cols<kSubCols, kBf16, kSoftcap, true, false, true>(sv, dpv, l2r, dlr, 0.f, 0.f, p.scale_log2,
-                                                                               p.softcap_pre, 0, 0, pk_p, pk_ds);
+          // with the cap the second half needs the tanh of the first: both halves run per 16 columns once S^T and
+          // dP^T are complete, and nothing is carried across
+          if (!ptx::mbar_wait(s_full, par, abort_flag, 61)) { alive = false; break; }
+          if (!ptx::mbar_wait(dp_full, par, abort_flag, 65)) { alive = false; break; }
+          if (!ptx::mbar_wait(ds_free, par ^ 1u, abort_flag, 66)) { alive = false; break; }
+          ptx::tc_fence_after();
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t sv[16], dpv[16];
+            ptx::tmem_ld16(s_t + half * 16, sv);
+            ptx::tmem_ld16(dp_t + half * 16, dpv);
+            ptx::tmem_wait_ld();
+            uint32_t pk_p[8], pk_ds[8];
+            softmax_backward_cols<16, kBf16, true, true, true, true>(sv, dpv, stats + half * 16, stats + kTile + half * 16,
+                                                                     0.f, 0.f, p.scale_log2, p.softcap_pre,
+                                                                     masked ? lo - half * 16 : -(1 << 30),
+                                                                     masked ? hi - half * 16 : (1 << 30), pk_p, pk_ds);
+            ptx::tmem_st8(s_t + half * 8, pk_p);
+            const int piece = ds_piece0 + 2 * half;
+            ptx::st_shared_v4(ds_row + ((piece ^ (row & 7)) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
+            ptx::st_shared_v4(ds_row + (((piece + 1) ^ (row & 7)) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
+          }
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive_warp(p_full);
         }
-        // P^T goes back to tensor memory, to the start of this warp's own (already loaded) S^T columns; dS^T goes to
-        // shared memory, where it is the A operand of dK (keys x queries) and the B operand of dQ^T
-        ptx::tmem_st8(st_t, pk_p);
-        uint8_t* ds_tile = sDs + u * Cfg::kDsBytes;
-        ptx::st_shared_v4(ds_tile + ds_off0, pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
-        ptx::st_shared_v4(ds_tile + ds_off1, pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
         if (threadIdx.x == 0) {
-          dq_desc[2 * u] = hdr0 & 1;
-          dq_desc[2 * u + 1] = hdr2;
+          dq_desc[2 * par] = hdr0 & ~6;
+          dq_desc[2 * par + 1] = hdr2;
         }
         ptx::fence_async_smem();
-        ptx::tmem_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive_warp(&pds_full[u]);
+        ptx::mbar_arrive_warp(ds_full);
+        if (threadIdx.x == 0) FDA_TRACE_PUT(10, gc);
       }
     }
   }
@@ -430,62 +614,53 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
 }
 
 // ------------------------------------------------------------------------------------------------------------
-// dQ = round(accumulator * softmax_scale), transposed back to rows of queries. One block per 64-row sub-tile of a
-// (sample, head, half); stands where the reference converts its accumulator
-// (csrc/fda/flash_bwd_postprocess_kernel.h:160-264 there).
+// dQ = round(accumulator * softmax_scale). One block per 64 query rows of a (sample, head, half); stands where the
+// reference converts its accumulator (csrc/fda/flash_bwd_postprocess_kernel.h:160-264 there).
 // ------------------------------------------------------------------------------------------------------------
 template <int kHeadDim, bool kBf16>
 __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const __grid_constant__ BwdParams p) {
-  __shared__ float tile[kHeadDim][kSub + 1];
-  const int t = blockIdx.x;            // sub-tile of the half
   const int h = blockIdx.y >> 1, half = blockIdx.y & 1;
   const int b = blockIdx.z;
   const Sample sm = sample_of(p, b);
-  const int sa = t * kSub;
-  if (sa >= sm.n) return;
+  const int qa = blockIdx.x * 64;
+  if (qa >= sm.n) return;
   const int grow0 = p.cu_seqlens != nullptr ? sm.row0 : b * p.seqlen;
-  const float* src = p.dq_acc + (static_cast<size_t>(h) * p.acc_tiles + acc_tile_of(grow0, sm.n, b, half, sa)) *
-                                    (kSub * kHeadDim);
-  // accumulator tile: [head dim][64 queries]; 16 threads read one row of 64 floats
-  for (int r = threadIdx.x / 16; r < kHeadDim; r += 16) {
-    const float4 v = *reinterpret_cast<const float4*>(src + r * kSub + (threadIdx.x % 16) * 4);
-    const int c = (threadIdx.x % 16) * 4;
-    tile[r][c] = v.x; tile[r][c + 1] = v.y; tile[r][c + 2] = v.z; tile[r][c + 3] = v.w;
-  }
-  __syncthreads();
-  // output: 64 query rows x head_dim values, 8 values (16 bytes) per thread and step
+  const float* src =
+      p.dq_acc + (static_cast<size_t>(h) * p.acc_tiles * 64 + acc_row_of(grow0, sm.n, b, half, qa)) * kHeadDim;
+  // a thread turns 8 consecutive values of a row into one 16-byte store
   constexpr int kPieces = kHeadDim / 8;
-  for (int i = threadIdx.x; i < kSub * kPieces; i += 256) {
-    const int qr = i / kPieces, piece = i % kPieces;
-    if (sa + qr >= sm.n || piece * 8 >= p.head_dim) continue;
-    uint32_t w[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      w[j] = ptx::pack2<kBf16>(tile[piece * 8 + 2 * j][qr] * p.softmax_scale,
-                               tile[piece * 8 + 2 * j + 1][qr] * p.softmax_scale);
-    }
-    const int64_t srow = static_cast<int64_t>(sm.row0) + half * sm.n + sa + qr;
+  for (int i = threadIdx.x; i < 64 * kPieces; i += 256) {
+    const int qr = i / kPieces, piece = i % kPieces;
+    if (qa + qr >= sm.n || piece * 8 >= p.head_dim) continue;
+    // blocks of 32 rows are stored [head dim / 32][32 rows][32 values]
+    const float* s8 = src + (qr / 32) * (32 * kHeadDim) + (piece / 4) * 1024 + (qr % 32) * 32 + (piece % 4) * 8;
+    const float4 lo = *reinterpret_cast<const float4*>(s8);
+    const float4 hi = *reinterpret_cast<const float4*>(s8 + 4);
+    const float sc = p.softmax_scale;
+    const int64_t srow = static_cast<int64_t>(sm.row0) + half * sm.n + qa + qr;
     uint16_t* dst = static_cast<uint16_t*>(p.dq) + sm.bcoord * p.dq_bs + srow * p.dq_rs + h * p.dq_hs + piece * 8;
-    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(dst) = make_uint4(ptx::pack2<kBf16>(lo.x * sc, lo.y * sc), ptx::pack2<kBf16>(lo.z * sc, lo.w * sc),
+                                                ptx::pack2<kBf16>(hi.x * sc, hi.y * sc), ptx::pack2<kBf16>(hi.z * sc, hi.w * sc));
   }
 }
 
-template <int kHeadDim, int kStages, bool kBf16, bool kSoftcap>
+template <int kHeadDim, int kSlots, int kDoSlots, bool kBf16, bool kSoftcap>
 int launch_fused_instance(const BwdParams& p, int sm_count, unsigned stages, cudaStream_t stream) {
   if (stages & 2u) {
-    using Cfg = FusedCfg<kHeadDim, kStages>;
-    auto kernel = bwd_fused_kernel<kHeadDim, kStages, kBf16, kSoftcap>;
+    using Cfg = FusedCfg<kHeadDim, kSlots, kDoSlots>;
+    auto kernel = bwd_fused_kernel<kHeadDim, kSlots, kDoSlots, kBf16, kSoftcap>;
     static PerDeviceFlags smem_set;
     const int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
-    FDA_CUDA_TRY(cudaMemsetAsync(p.dq_acc, 0, static_cast<size_t>(p.heads) * p.acc_tiles * kSub * kHeadDim * 4, stream));
+    FDA_CUDA_TRY(cudaMemsetAsync(p.dq_acc, 0, static_cast<size_t>(p.heads) * p.acc_tiles * 64 * kHeadDim * 4, stream));
     const int items = p.tiles_per_half * 2 * p.heads_k * p.batch;
     const int grid = items < sm_count ? items : sm_count;
     kernel<<<grid, kDkdvThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
   if (stages & 4u) {
-    dim3 grid(p.n_pad / kSub, 2 * p.heads, p.batch);
+    dim3 grid(p.n_pad / 64, 2 * p.heads, p.batch);
     bwd_dq_convert_kernel<kHeadDim, kBf16><<<grid, 256, 0, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
   }
@@ -494,29 +669,30 @@ int launch_fused_instance(const BwdParams& p, int sm_count, unsigned stages, cud
 
 }  // namespace
 
-// Number of 64-row accumulator tiles per query head (see acc_tile_of): every half of every sample gets whole tiles.
+// Number of 64-row blocks of the dQ accumulator per query head (see acc_row_of): every half of every sample starts at
+// its own block, and the last 128-row step of a half may reach one block past the half's rows.
 int64_t bwd_fused_acc_tiles(const FdaProblem& pr) {
-  return static_cast<int64_t>(pr.total) / kSub + 2 * static_cast<int64_t>(pr.batch) + 1;
+  return static_cast<int64_t>(pr.total) / 64 + 2 * static_cast<int64_t>(pr.batch) + 3;
 }
 
 size_t bwd_fused_acc_bytes(const FdaProblem& pr) {
   const int d_round = pr.head_dim <= 64 ? 64 : 128;
-  return static_cast<size_t>(pr.heads) * bwd_fused_acc_tiles(pr) * kSub * d_round * 4;
+  return static_cast<size_t>(pr.heads) * bwd_fused_acc_tiles(pr) * 64 * d_round * 4;
 }
 
-// stages: bit 1 = accumulator zero-fill + fused kernel, bit 2 = dQ convert.
+// stages: bit 1 = accumulator zero-fill + single-pass kernel, bit 2 = dQ convert.
 int launch_bwd_fused(const BwdParams& p, int d_round, bool bf16, bool softcap, int sm_count, unsigned stages,
                      cudaStream_t stream) {
   if (d_round == 64) {
-    if (bf16) return softcap ? launch_fused_instance<64, 6, true, true>(p, sm_count, stages, stream)
-                             : launch_fused_instance<64, 6, true, false>(p, sm_count, stages, stream);
-    return softcap ? launch_fused_instance<64, 6, false, true>(p, sm_count, stages, stream)
-                   : launch_fused_instance<64, 6, false, false>(p, sm_count, stages, stream);
+    if (bf16) return softcap ? launch_fused_instance<64, 3, 3, true, true>(p, sm_count, stages, stream)
+                             : launch_fused_instance<64, 3, 3, true, false>(p, sm_count, stages, stream);
+    return softcap ? launch_fused_instance<64, 3, 3, false, true>(p, sm_count, stages, stream)
+                   : launch_fused_instance<64, 3, 3, false, false>(p, sm_count, stages, stream);
   }
-  if (bf16) return softcap ? launch_fused_instance<128, 3, true, true>(p, sm_count, stages, stream)
-                           : launch_fused_instance<128, 3, true, false>(p, sm_count, stages, stream);
-  return softcap ? launch_fused_instance<128, 3, false, true>(p, sm_count, stages, stream)
-                 : launch_fused_instance<128, 3, false, false>(p, sm_count, stages, stream);
+  if (bf16) return softcap ? launch_fused_instance<128, 2, 1, true, true>(p, sm_count, stages, stream)
+                           : launch_fused_instance<128, 2, 1, true, false>(p, sm_count, stages, stream);
+  return softcap ? launch_fused_instance<128, 2, 1, false, true>(p, sm_count, stages, stream)
+                 : launch_fused_instance<128, 2, 1, false, false>(p, sm_count, stages, stream);
 }
 
 int read_status_bwd_fused(int32_t* out4) {

@@ -1036,6 +1036,7 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
     if (a.workspace_bytes < bwd_workspace_bytes(pr)) return FDA_ERR_WORKSPACE;
     p.dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + 2 * one + 256);
     p.acc_tiles = static_cast<int>(bwd_fused_acc_tiles(pr));
+    p.acc_floats = static_cast<int64_t>(bwd_fused_acc_bytes(pr) / 4);
   }
   if (stage_mask & 6u) FDA_CUDA_TRY(cudaMemsetAsync(p.ticket_kv, 0, 256, stream));
   const bool softcap = pr.softcap > 0.f;

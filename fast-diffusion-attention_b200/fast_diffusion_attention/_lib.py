@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfda_sm100.so")
+# FDA_LIBRARY names another build of the same library (for instance one compiled with -lineinfo off or with
+# ptxas statistics); by default the in-tree build next to this file is loaded.
+LIB_PATH = os.environ.get("FDA_LIBRARY") or os.path.join(_HERE, "libfda_sm100.so")
 
 FDA_BF16, FDA_FP16, FDA_E4M3 = 0, 1, 2
 
