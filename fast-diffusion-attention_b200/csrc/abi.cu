@@ -164,6 +164,10 @@ int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int
   return c;
 }
 
+int fda_selftest_wait(long long limit_cycles, void* stream) {
+  return fda::launch_selftest_wait(limit_cycles, static_cast<cudaStream_t>(stream));
+}
+
 int fda_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, void* stream) {
   return fda::launch_selftest_umma(mode, a, b, c, n, k, static_cast<cudaStream_t>(stream));
 }

@@ -10,10 +10,11 @@
 //   dQ^T = K^T dS^T                     head dim on lanes, 128 query columns, written over the consumed dP^T buffer
 // The two halves of the arithmetic hang on different products, so they overlap different MMAs: P^T is computed while
 // dP^T (and the tail of the previous step) runs, dS^T while dV runs. The partial dQ^T of a step is added into an fp32
-// accumulator in global memory (red.global.add.f32, one 128-byte line per warp instruction);
-// `bwd_dq_convert_kernel` then scales and rounds it into dQ. The accumulator holds rows of queries ([rows][head dim]
-// per query head): a thread of the drain warps owns one head-dim row of dQ^T, so a warp adds 32 consecutive floats
-// of one query row per instruction.
+// accumulator in global memory: the drain warps move it from tensor memory through a small shared-memory staging
+// area and out as 4 KB bulk reductions (cp.reduce.async.bulk add.f32); `bwd_dq_convert_kernel` then scales and
+// rounds the accumulator into dQ. About 30 bytes per clock leave an SM towards L2 whatever the instruction (plain
+// red, vector red and bulk reductions measured alike), so the 64 KB of a step take about 2200 cycles: the drain is
+// the long pole of the chain dP^T -> dS^T -> dQ^T -> drain -> next dP^T.
 //
 // The reference does the same five GEMMs per pair with an fp32 dQ accumulator reduced through global memory
 // (csrc/fda/mainloop_bwd_sm90_tma_gmma_ws.hpp:815-984 `bwd_step`, :605-664 `store_dq`, there with
@@ -22,15 +23,6 @@
 // backward keeps the two-kernel split (dK/dV kernel + dQ kernel), which has no cross-CTA reduction.
 #include "bwd_common.cuh"
 
-#ifdef FDA_TRACE
-__device__ long long g_fda_trace[16 * 256];
-extern "C" int fda_debug_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_fda_trace, sizeof(long long) * 16 * 256) == cudaSuccess ? 0 : 1;
-}
-#define FDA_TRACE_PUT(row, idx) do { if (blockIdx.x == 0 && (idx) < 256u) g_fda_trace[(row) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define FDA_TRACE_PUT(row, idx) do { } while (0)
-#endif
 
 namespace fda {
 namespace {
@@ -206,7 +198,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         const int rows_left = flags >> 8;   // query rows of this tile that exist (1..128)
         if (!ptx::mbar_wait(dq_full, par, abort_flag, 64)) { alive = false; break; }
         ptx::tc_fence_after();
-        if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(11, gd);
         // Blocks of 32 query rows of the accumulator are stored as [head dim / 32][32 queries][32 head-dim values]: a
         // warp's 32 x 32 piece of dQ^T goes through shared memory (a thread writes its head-dim value of each query,
         // 32 lanes = 128 consecutive bytes) and out as ONE 4 KB bulk reduction, issued by lane 0. Two staging slots per
@@ -225,14 +216,12 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
             if (c == 3) {
               ptx::tc_fence_before();
               ptx::mbar_arrive_warp(dp_free);
-              if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(12, gd);
             }
             if (c * 32 < rows_left) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) stage[i * 32 + lane] = __uint_as_float(a[i]);
               ptx::fence_async_smem();
               __syncwarp();
-#ifndef FDA_NORED
               if (lane == 0) {
                 float* target = dst + c * (32 * kHeadDim);
                 if (target >= p.dq_acc && target + 1024 <= p.dq_acc + p.acc_floats) {
@@ -244,14 +233,12 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
                   g_fda_status[3] = flags;
                 }
               }
-#endif
               ++n_bulk;
             }
           }
         } else {
           ptx::mbar_arrive_warp(dp_free);
         }
-        if (warp == kEpiWarp0 && lane == 0) FDA_TRACE_PUT(13, gd);
       }
       if (!alive) break;
       const int kj = it.k0 + row;
@@ -369,7 +356,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           last = (hdr[4 * slot] & 1) != 0;
           if (!ptx::mbar_wait(s_free, (g & 1u) ^ 1u, abort_flag, 54)) { alive = false; break; }
           ptx::tc_fence_after();
-          FDA_TRACE_PUT(0, g);
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
             const uint32_t off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
@@ -380,7 +366,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           if (!ptx::mbar_wait(&do_full[dslot], (g / kDoSlots) & 1u, abort_flag, 56)) { alive = false; break; }
           if (!ptx::mbar_wait(dp_free, (g & 1u) ^ 1u, abort_flag, 58)) { alive = false; break; }
           ptx::tc_fence_after();
-          FDA_TRACE_PUT(1, g);
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
             const uint32_t off = ((kk / 4) * T::kPanelBytes + (kk % 4) * 32) >> 4;
@@ -389,7 +374,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           }
           ptx::umma_commit(dp_full);
           ptx::umma_commit(&do_empty[dslot]);
-          FDA_TRACE_PUT(2, g);
         }
         ++n_item;
       }
@@ -424,7 +408,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           last = (hdr[4 * slot] & 1) != 0;
           if (!ptx::mbar_wait(p_full, g & 1u, abort_flag, 53)) { alive = false; break; }
           ptx::tc_fence_after();
-          FDA_TRACE_PUT(3, g);
           // dV += P^T dO: P^T of the 16 queries of reduction step kk sits at column 32 (kk / 2) + 8 (kk % 2)
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
@@ -434,10 +417,8 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           }
           ptx::umma_commit(s_free);
           ptx::umma_commit(&do_empty[g % kDoSlots]);
-          FDA_TRACE_PUT(4, g);
           if (!ptx::mbar_wait(ds_full, g & 1u, abort_flag, 59)) { alive = false; break; }
           ptx::tc_fence_after();
-          FDA_TRACE_PUT(5, g);
           // dQ^T before dK: its drain (tensor memory -> registers -> global adds) then runs under dK
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
@@ -455,7 +436,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           acc = true;
           ptx::umma_commit(&q_empty[slot]);
           ptx::umma_commit(ds_free);
-          FDA_TRACE_PUT(6, g);
         }
         if (!alive) break;
         ptx::umma_commit(acc_full);
@@ -502,7 +482,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           float pr[kCols];   // the step's probabilities of this thread, kept from the first half of the arithmetic
           if (!ptx::mbar_wait(s_full, par, abort_flag, 61)) { alive = false; break; }
           ptx::tc_fence_after();
-          if (threadIdx.x == 0) FDA_TRACE_PUT(7, gc);
           {
             uint32_t sv[kCols];
             ptx::tmem_ld16(s_t, sv);
@@ -543,12 +522,10 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           ptx::tmem_wait_st();
           ptx::tc_fence_before();
           ptx::mbar_arrive_warp(p_full);
-          if (threadIdx.x == 0) FDA_TRACE_PUT(8, gc);
           if (!ptx::mbar_wait(dp_full, par, abort_flag, 65)) { alive = false; break; }
           // dQ^T and dK of the previous step have read the dS^T tile (long ago in the steady state)
           if (!ptx::mbar_wait(ds_free, par ^ 1u, abort_flag, 66)) { alive = false; break; }
           ptx::tc_fence_after();
-          if (threadIdx.x == 0) FDA_TRACE_PUT(9, gc);
           {
             uint32_t dpv[kCols];
             ptx::tmem_ld16(dp_t, dpv);
@@ -604,7 +581,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         ptx::fence_async_smem();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(ds_full);
-        if (threadIdx.x == 0) FDA_TRACE_PUT(10, gc);
       }
     }
   }

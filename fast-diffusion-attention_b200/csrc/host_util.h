@@ -130,6 +130,7 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream);
 int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask);
 int launch_bwd_noalloc(const FdaBwdArgs& a, cudaStream_t stream);
 int launch_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, cudaStream_t stream);
+int launch_selftest_wait(long long limit_cycles, cudaStream_t stream);
 int read_status_fwd(int32_t* out4);
 int read_status_bwd(int32_t* out4);
 int read_status_bwd_fused(int32_t* out4);

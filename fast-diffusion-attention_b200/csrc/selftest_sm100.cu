@@ -135,8 +135,49 @@ __global__ void __launch_bounds__(128, 1) selftest_umma_kernel(const __grid_cons
 }
 
 
+// A wait that nobody ends: one block allocates tensor memory the way the attention kernels do, one thread waits on a
+// barrier no one arrives at with a SHORT limit, the others see the abort flag in their own wait, and everybody takes
+// the kernels' exit path (drain, free the tensor memory, return). Exercises ptx::mbar_wait's give-up branch, which
+// in the attention kernels is two seconds away.
+__global__ void __launch_bounds__(128, 1) selftest_wait_kernel(long long limit_cycles) {
+  __shared__ uint64_t never;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(&never, 1);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 0) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  // thread 0 gives up after limit_cycles and raises the flag; the others wait with the production limit and leave
+  // as soon as they see the flag
+  const bool ok = ptx::mbar_wait(&never, 0, &abort_flag, 110, threadIdx.x == 0 ? limit_cycles : ptx::kWaitLimitCycles);
+  (void)ok;
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) ptx::tmem_dealloc(tmem, 512);
+}
+
 }  // namespace
 
+int launch_selftest_wait(long long limit_cycles, cudaStream_t stream) {
+  if (limit_cycles < 1000 || limit_cycles > 100000000LL) return FDA_ERR_SHAPE;   // at most ~50 ms
+  DeviceInfo info;
+  int rc = current_device_info(&info);
+  if (rc) return rc;
+  if (info.cc_major != 10) return FDA_ERR_ARCH;
+  selftest_wait_kernel<<<1, 128, 0, stream>>>(limit_cycles);
+  FDA_CUDA_TRY(cudaGetLastError());
+  return FDA_OK;
+}
 
 int launch_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, cudaStream_t stream) {
   if (!a || !b || !c) return FDA_ERR_NULL;

@@ -50,7 +50,7 @@ class FdaBwdArgs(C.Structure):
 EXPORTS = [
     "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_bwd_stages", "fda_bwd_noalloc", "fda_strerror",
     "fda_last_cuda_error", "fda_device_status", "fda_version", "fda_geom_key_plan", "fda_geom_query_plan",
-    "fda_geom_classify", "fda_selftest_umma",
+    "fda_geom_classify", "fda_selftest_umma", "fda_selftest_wait",
 ]
 
 _lib = None
@@ -92,6 +92,8 @@ def load():
     lib.fda_geom_classify.argtypes = [C.c_int] * 10
     lib.fda_selftest_umma.restype = C.c_int
     lib.fda_selftest_umma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    lib.fda_selftest_wait.restype = C.c_int
+    lib.fda_selftest_wait.argtypes = [C.c_longlong, C.c_void_p]
     _lib = lib
     return lib
 

@@ -21,8 +21,22 @@ if hasattr(torch, "float8_e4m3fn"):
     _DTYPES[torch.float8_e4m3fn] = _lib.FDA_E4M3
 
 
+def _tile_copy_friendly(x):
+    """The kernels move tiles with TMA and rows with 16-byte vector accesses: the base address and every stride
+    but the last must be multiples of 16 bytes."""
+    size = x.element_size()
+    return x.data_ptr() % 16 == 0 and all((st * size) % 16 == 0 for st, n in zip(x.stride()[:-1], x.shape[:-1]) if n > 1)
+
+
 def maybe_contiguous(x):
-    return x.contiguous() if x is not None and x.stride(-1) != 1 else x
+    """The reference copies an input only when its last dimension is strided (interface.py:17-18 there, its kernels
+    take any other strides). Here a view whose base or strides are not 16-byte multiples (say x[..., 4:68]) is
+    copied as well, so that every call the reference accepts is accepted."""
+    if x is None:
+        return x
+    if x.stride(-1) != 1 or (x.dim() >= 3 and not _tile_copy_friendly(x)):
+        return x.contiguous()
+    return x
 
 
 def _tensor_view(t: torch.Tensor, varlen: bool) -> _lib.FdaTensor:
@@ -193,8 +207,23 @@ def backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_
     for name, g, ref in (("dq", dq, q), ("dk", dk, k), ("dv", dv, v)):
         if g.dtype != q.dtype or g.shape != ref.shape or g.stride(-1) != 1:
             raise RuntimeError(f"{name} must have the dtype and shape of its input and a contiguous last dimension")
+    # the same checks as mha_bwd makes on its arguments (csrc/fda/flash_api.cpp:491, :523-529 of the reference): the
+    # kernels index these tensors without looking at them again
+    for name, t in (("out", out), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv), ("softmax_lse", softmax_lse)):
+        if t.device != q.device:
+            raise RuntimeError(f"{name} must be on the same device as q")
+    if softmax_lse.dtype != torch.float32:
+        raise RuntimeError("softmax_lse must have dtype float32")
+    want_lse = (heads, total) if varlen else (batch, heads, seqlen)
+    if tuple(softmax_lse.shape) != want_lse:
+        raise RuntimeError(f"softmax_lse must have shape {want_lse}")
     if not softmax_lse.is_contiguous():
         raise RuntimeError("softmax_lse must be contiguous")
+    if varlen and tuple(cu_seqlens.shape) != (batch + 1,):
+        raise RuntimeError("cu_seqlens must have shape (batch_size + 1,)")
+    for name, g in (("dq", dq), ("dk", dk), ("dv", dv)):
+        if not _tile_copy_friendly(g):
+            raise RuntimeError(f"{name} must have a 16-byte aligned base address and row/head/batch strides")
     if softmax_scale is None:
         softmax_scale = head_dim ** (-0.5)
     n_pad = _padded_half(seqlen)

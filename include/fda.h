@@ -174,6 +174,16 @@ int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int
  * at most 128 (k) / 256 (n). */
 int fda_selftest_umma(int mode, const void* a, const void* b, float* c, int n, int k, void* stream);
 
+/* ---- bounded-wait self test (GPU) ------------------------------------------------------------------------- */
+/* Launches one block whose wait on a barrier nobody arrives at gives up after `limit_cycles` SM clocks (1e3 .. 1e8),
+ * then leaves through the kernels' ordinary exit path (tensor memory freed, kernel returns). Afterwards
+ * fda_device_status() reports FDA_ERR_DEVICE_WAIT with code 110 once, and the device is as usable as before.
+ * Every device-side wait of the library is bounded in this way (the kernels' own limit is about two seconds); when
+ * fda_device_status() reports an expired wait the outputs of the calls since the last check are undefined.
+ * No counterpart in the reference, whose deterministic backward spins without a bound
+ * (csrc/fda/mainloop_bwd_sm90_tma_gmma_ws.hpp:641-644). */
+int fda_selftest_wait(long long limit_cycles, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -67,11 +67,15 @@ def main(root):
         dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
         o_pt, lse_pt = ref.attention_ref(q, k, v, bs, softmax_scale=scale, softcap=cap, upcast=False,
                                          reorder_ops=True)
-        rec = dict(seed=1000 + idx, out=o, lse=lse, dq=dq, dk=dk, dv=dv, out_pt=o_pt, lse_pt=lse_pt)
+        # gradients of the same-precision evaluation: what the reference's tests take as "plain PyTorch" for dq, dk, dv
+        # (tests/test_diffusion_attn.py:85-104 there: autograd through attention_ref(upcast=False, reorder_ops=True))
+        dq_pt, dk_pt, dv_pt = torch.autograd.grad(o_pt, (q, k, v), do)
+        rec = dict(seed=1000 + idx, out=o, lse=lse, dq=dq, dk=dk, dv=dv, out_pt=o_pt, lse_pt=lse_pt,
+                   dq_pt=dq_pt, dk_pt=dk_pt, dv_pt=dv_pt)
+        strided = ("out", "dq", "dk", "dv", "out_pt", "dq_pt", "dk_pt", "dv_pt")
         if name == "c1_cpu_config":
             # keep the fixture small: every ROW_STRIDE-th sequence position of the largest case
-            rec = {key: (val[:, ::ROW_STRIDE] if key in ("out", "dq", "dk", "dv", "out_pt") else val)
-                   for key, val in rec.items()}
+            rec = {key: (val[:, ::ROW_STRIDE] if key in strided else val) for key, val in rec.items()}
         out[name] = rec
     for idx, (name, (ns, H, Hk, d, bs, cap, dt)) in enumerate(VARLEN_CASES.items()):
         dtype = getattr(torch, dt)

@@ -34,12 +34,13 @@ def _randn(shape, seed, dtype=torch.bfloat16):
 def _grads(q, k, v, do, bs, cu=None, max_n=None, **kw):
     q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
     if cu is None:
-        out = diffusion_attn_func(q, k, v, bs, **kw)
+        out, lse = diffusion_attn_func(q, k, v, bs, return_attn_probs=True, **kw)
     else:
-        out = diffusion_attn_varlen_func(q, k, v, cu, cu, max_n, max_n, bs, **kw)
+        out, lse = diffusion_attn_varlen_func(q, k, v, cu, cu, max_n, max_n, bs, return_attn_probs=True, **kw)
     out.backward(do)
     torch.cuda.synchronize()
     assert _lib.device_status()[0] == 0
+    _grads.lse = lse.detach()   # (batch, heads, rows) or (heads, total): checked by _check_slice
     return out.detach(), q.grad, k.grad, v.grad
 
 
@@ -73,9 +74,14 @@ def _oracle_slice(q, k, v, do, bs, hk, group, softcap=0.0):
     return hs, out_t, out_p, lse_t, g_t, g_p
 
 
-def _check_slice(name, q, k, v, do, out, dq, dk, dv, bs, hk, group, softcap=0.0):
-    hs, out_t, out_p, _, g_t, g_p = _oracle_slice(q, k, v, do, bs, hk, group, softcap)
+def _check_slice(name, q, k, v, do, out, dq, dk, dv, bs, hk, group, softcap=0.0, lse=None):
+    """`lse`: the log-sum-exp rows of the same sample, (heads, rows)."""
+    hs, out_t, out_p, lse_t, g_t, g_p = _oracle_slice(q, k, v, do, bs, hk, group, softcap)
     assert_within_2x(name + " out", out[:, :, hs], out_t, out_p)
+    assert lse is not None
+    # natural-log units, float32; the tolerance of the reference's tests (tests/test_diffusion_attn.py:98 there,
+    # 2 x the plain error + 1e-4) with the plain error bounded by bf16 rounding of scores of this magnitude
+    assert (lse[hs].float() - lse_t[0].float()).abs().max().item() <= 2e-2, name + " lse"
     assert_within_2x(name + " dq", dq[:, :, hs], g_t[0], g_p[0])
     assert_within_2x(name + " dk", dk[:, :, hk:hk + 1], g_t[1], g_p[1])
     assert_within_2x(name + " dv", dv[:, :, hk:hk + 1], g_t[2], g_p[2])
@@ -88,7 +94,7 @@ def test_mha_bf16_d128_block256():
     out, dq, dk, dv = _grads(q, k, v, do, bs)
     for b in (0, B - 1):
         _identities(q[b], k[b], v[b], do[b], out[b], dq[b], dk[b], dv[b], 1)
-    _check_slice("C2", q[3:4], k[3:4], v[3:4], do[3:4], out[3:4], dq[3:4], dk[3:4], dv[3:4], bs, 5, 1)
+    _check_slice("C2", q[3:4], k[3:4], v[3:4], do[3:4], out[3:4], dq[3:4], dk[3:4], dv[3:4], bs, 5, 1, lse=_grads.lse[3])
     ones = diffusion_attn_func(q, k, torch.ones_like(v), bs)
     assert (ones.float() - 1).abs().max().item() <= 2 ** -7
     # mask: clean block 3 is seen by noisy blocks 4.. and clean blocks 3..; noisy block 2 only by itself
@@ -115,11 +121,13 @@ def test_gqa_bf16_d128_block1024_deterministic():
     q, do = _randn((B, 2 * n, H, d), 11), _randn((B, 2 * n, H, d), 12)
     k, v = _randn((B, 2 * n, Hk, d), 13), _randn((B, 2 * n, Hk, d), 14)
     out, dq, dk, dv = _grads(q, k, v, do, bs, deterministic=True)
+    lse_c3 = _grads.lse
     out_b, dq_b, dk_b, dv_b = _grads(q, k, v, do, bs, deterministic=True)
     for a, b in ((out, out_b), (dq, dq_b), (dk, dk_b), (dv, dv_b)):
         assert torch.equal(a, b)
     _identities(q[1], k[1], v[1], do[1], out[1], dq[1], dk[1], dv[1], H // Hk)
-    _check_slice("C3", q[2:3], k[2:3], v[2:3], do[2:3], out[2:3], dq[2:3], dk[2:3], dv[2:3], bs, 6, H // Hk)
+    _check_slice("C3", q[2:3], k[2:3], v[2:3], do[2:3], out[2:3], dq[2:3], dk[2:3], dv[2:3], bs, 6, H // Hk,
+                 lse=lse_c3[2])
 
 
 def test_varlen_bf16_d64_block256_softcap():
@@ -138,7 +146,8 @@ def test_varlen_bf16_d64_block256_softcap():
         _identities(q[lo:hi], k[lo:hi], v[lo:hi], do[lo:hi], out[lo:hi], dq[lo:hi], dk[lo:hi], dv[lo:hi], 1)
     lo, hi = int(cu[big]), int(cu[big + 1])
     sl = lambda t: t[lo:hi].unsqueeze(0)
-    _check_slice("C4", sl(q), sl(k), sl(v), sl(do), sl(out), sl(dq), sl(dk), sl(dv), bs, 17, 1, softcap=softcap)
+    _check_slice("C4", sl(q), sl(k), sl(v), sl(do), sl(out), sl(dq), sl(dk), sl(dv), bs, 17, 1, softcap=softcap,
+                 lse=_grads.lse[:, lo:hi])
 
 
 def test_d256_bf16_and_fp8_forward():
@@ -147,8 +156,9 @@ def test_d256_bf16_and_fp8_forward():
     B, n, H, d, bs = 2, 8192, 8, 256, 256
     q, k, v, do = (_randn((B, 2 * n, H, d), s) for s in (31, 32, 33, 34))
     out, dq, dk, dv = _grads(q, k, v, do, bs)
+    lse_c5 = _grads.lse
     _identities(q[0], k[0], v[0], do[0], out[0], dq[0], dk[0], dv[0], 1)
-    _check_slice("C5", q[1:2], k[1:2], v[1:2], do[1:2], out[1:2], dq[1:2], dk[1:2], dv[1:2], bs, 2, 1)
+    _check_slice("C5", q[1:2], k[1:2], v[1:2], do[1:2], out[1:2], dq[1:2], dk[1:2], dv[1:2], bs, 2, 1, lse=lse_c5[1])
 
     def quantise(t):
         amax = t.float().abs().amax(dim=(1, 3))                  # (B, heads)

@@ -59,6 +59,19 @@ def test_dense_oracle_matches_golden(name):
     out_pt, lse_pt = orc.forward(q, k, v, bs, softmax_scale=scale, softcap=cap, compute_dtype=dtype)
     want = torch.from_numpy(gold[f"{name}/out_pt"])
     assert torch.allclose(sub(out_pt).float(), want, **tol)
+    # ... and of the gradients: the oracle's same-precision backward sets the tolerance of dq, dk, dv in the GPU tests,
+    # so its error must be the error of the reference's own plain arm (autograd through
+    # attention_ref(upcast=False, reorder_ops=True)), not a looser one
+    plain = orc.backward(q, k, v, do, bs, softmax_scale=scale, softcap=cap, compute_dtype=dtype)
+    for key, val in zip(("dq", "dk", "dv"), plain):
+        truth = torch.from_numpy(gold[f"{name}/{key}"])
+        e_oracle = sub(val).float() - truth
+        e_ref = torch.from_numpy(gold[f"{name}/{key}_pt"]) - truth
+        # the root-mean-square errors agree to a percent; the maxima are single elements, a whole number of
+        # 16-bit rounding steps each, so they may differ by one step
+        rms_oracle, rms_ref = e_oracle.pow(2).mean().sqrt().item(), e_ref.pow(2).mean().sqrt().item()
+        assert rms_oracle <= 1.1 * rms_ref + 1e-6, (name, key, rms_oracle, rms_ref)
+        assert e_oracle.abs().max().item() <= 1.5 * e_ref.abs().max().item() + 1e-5, (name, key)
 
 
 @pytest.mark.parametrize("name", list(VARLEN_CASES))
