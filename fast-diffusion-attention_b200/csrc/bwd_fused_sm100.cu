@@ -407,6 +407,9 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           if (!ptx::mbar_wait(&q_full[slot], spar, abort_flag, 55)) { alive = false; break; }
           last = (hdr[4 * slot] & 1) != 0;
           if (!ptx::mbar_wait(p_full, g & 1u, abort_flag, 53)) { alive = false; break; }
+          // dO usually landed long ago (dP^T of this step reads it too), but nothing this thread has waited for so far
+          // says so
+          if (!ptx::mbar_wait(&do_full[g % kDoSlots], (g / kDoSlots) & 1u, abort_flag, 67)) { alive = false; break; }
           ptx::tc_fence_after();
           // dV += P^T dO: P^T of the 16 queries of reduction step kk sits at column 32 (kk / 2) + 8 (kk % 2)
 #pragma unroll

@@ -75,6 +75,8 @@ def _check_inputs(q, k, v, cu_seqlens, max_seqlen, block_size, backward=False):
             raise RuntimeError("cu_seqlens must have dtype torch.int32")
         if not cu_seqlens.is_cuda or not cu_seqlens.is_contiguous():
             raise RuntimeError("cu_seqlens must be a contiguous CUDA tensor")
+        if cu_seqlens.dim() != 1 or cu_seqlens.numel() < 1:
+            raise RuntimeError("cu_seqlens must be one-dimensional with batch_size + 1 entries")
         if max_seqlen is None:
             raise RuntimeError("max_seqlen must be provided if cu_seqlens is provided")
         if q.dim() != 3:
@@ -193,8 +195,9 @@ def _diffusion_attn_forward_fake(
 
 def backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_seqlens=None, max_seqlen=None,
                     softmax_scale=None, softcap=0.0, deterministic=False, sm_margin=0, workspace=None, stages=7):
-    """Validate, size the workspace and enqueue the backward stages selected by `stages` (bit 0 preprocess,
-    bit 1 dK/dV, bit 2 dQ; 7 = the whole backward) on the current stream. A caller that times or profiles single
+    """Validate, size the workspace and enqueue the backward stages selected by `stages` (bit 0 preprocess, bit 1 the
+    single-pass kernel or the dK/dV kernel, bit 2 the dQ conversion or the dQ kernel, bit 3 forces the split form;
+    7 = the whole backward) on the current stream. A caller that times or profiles single
     stages passes the same `workspace` to every call. Returns the (batch, heads, 2, n_pad) view of rowsum(dO*O)."""
     dout, q, k, v, out = [maybe_contiguous(x) for x in (dout, q, k, v, out)]
     batch, seqlen, total = _check_inputs(q, k, v, cu_seqlens, max_seqlen, block_size, backward=True)
@@ -219,8 +222,6 @@ def backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_
         raise RuntimeError(f"softmax_lse must have shape {want_lse}")
     if not softmax_lse.is_contiguous():
         raise RuntimeError("softmax_lse must be contiguous")
-    if varlen and tuple(cu_seqlens.shape) != (batch + 1,):
-        raise RuntimeError("cu_seqlens must have shape (batch_size + 1,)")
     for name, g in (("dq", dq), ("dk", dk), ("dv", dv)):
         if not _tile_copy_friendly(g):
             raise RuntimeError(f"{name} must have a 16-byte aligned base address and row/head/batch strides")
