@@ -409,6 +409,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-other-configs", action="store_true")
     ap.add_argument("--skip-sustained", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the eager step only (for profilers)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -476,10 +477,62 @@ def main():
         raise SystemExit(f"device-side wait expired during warm-up: {status}")
 
     # ---- value: K steps, CUDA events on the launching (current) stream, max over ranks ------------------------------
+    # Eager: the Python calls are made every step. Their host cost (a few hundred microseconds of operator dispatch,
+    # autograd bookkeeping and argument marshalling) does not shrink with the slice, so with several ranks the eager
+    # step becomes launch-bound; the same calls captured once in a CUDA graph and replayed take the host out of the
+    # loop. Both are timed; `value` is the replayed one when the capture works, `eager` is reported beside it.
+    eager_ms_total = time_steps(step_public, args.steps, barrier)
+    host_enqueue_ms = None
+    barrier()
+    t_h = time.perf_counter()
+    for _ in range(args.steps):
+        step_public()
+    host_enqueue_ms = (time.perf_counter() - t_h) * 1e3 / args.steps    # time to ENQUEUE a step (no synchronisation)
+    barrier()
+    eager_ms = max_over_ranks(eager_ms_total, dist, world, dev) / args.steps
+    graph, graph_error = None, None
+    try:
+        if args.no_graph:
+            raise RuntimeError("--no-graph")
+        if hasattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch"):
+            torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step_public()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_outputs = step_public()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ref_outputs = step_public()
+        torch.cuda.synchronize()
+        for name, a, b in zip(("out", "dq", "dk", "dv"), graph_outputs, ref_outputs):
+            # the replay runs the same kernels: everything but dq (fp32 adds in scheduling order) is bitwise equal
+            if name != "dq" and not torch.equal(a, b):
+                raise RuntimeError(f"graph replay changed {name}")
+            if (a.float() - b.float()).abs().max().item() > 0.05 * b.float().abs().max().item() + 1e-3:
+                raise RuntimeError(f"graph replay changed {name}")
+    except Exception as e:   # pragma: no cover
+        graph, graph_error = None, str(e)[:200]
+    ok = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    use_graph = bool(ok.item() > 0)
     with ClockSampler(local_rank) as clocks:
-        total_ms = time_steps(step_public, args.steps, barrier)
+        if use_graph:
+            total_ms = time_steps(graph.replay, args.steps, barrier)
+        else:
+            total_ms = time_steps(step_public, args.steps, barrier)
     ms_per_step = max_over_ranks(total_ms, dist, world, dev) / args.steps
     value = step_flops / (ms_per_step * 1e-3) / 1e12
+    eager = dict(value=step_flops / (eager_ms * 1e-3) / 1e12, unit="TFLOPS", ms_per_step=eager_ms,
+                 host_enqueue_ms_per_step=host_enqueue_ms, cuda_graph="replayed" if use_graph else
+                 f"not used: {graph_error}")
 
     # ---- the same with scatter and gather inside the timed region (N > 1) ---------------------------------------------
     with_coll = None
@@ -697,7 +750,8 @@ def main():
                                 block_size=bs, global_batch=B,
                                 sharding=f"{kind}: {Hk // world if kind == 'heads' else Hk} key/value heads x "
                                          f"{B if kind == 'heads' else B // world} samples per rank",
-                                api="diffusion_attn_func + torch.autograd.grad, inputs resident on the device",
+                                api="diffusion_attn_func + torch.autograd.grad, inputs resident on the device" +
+                                    (", captured once in a CUDA graph and replayed" if use_graph else ", eager"),
                                 l2=f"a step reads and writes {1.07 / world:.2f} GB of tensors per rank plus a "
                                    f"{0.28 / world:.2f} GB fp32 dQ accumulator: more than the 126 MB L2, no flush used"),
                     per_gpu_tflops=value / world,
@@ -708,7 +762,7 @@ def main():
                     clocks=clocks.summary(), e2e=e2e, gpu_launches=4 * args.steps,
                     gpu_launches_note="forward, backward preprocess, single-pass backward, dQ convert per step (the two "
                                       "memsets of a step are the runtime's)",
-                    roofline=roofline, with_collectives=with_coll, replicas=replicas, sustained=sustained,
+                    eager=eager, roofline=roofline, with_collectives=with_coll, replicas=replicas, sustained=sustained,
                     other_configs=other, cpu_baseline=cpu)
         print(json.dumps(line), flush=True)
     if world > 1:

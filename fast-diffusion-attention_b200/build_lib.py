@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "fast_diffusion_attention", "libfda_sm100.so")
-SOURCES = ["abi.cu", "fwd_sm100.cu", "bwd_sm100.cu", "bwd_fused_sm100.cu", "selftest_sm100.cu"]
+SOURCES = ["abi.cu", "fwd_sm100.cu", "bwd_sm100.cu", "bwd_fused_sm100.cu", "selftest_sm100.cu", "varlen_list.cu"]
 
 
 def _nvcc():

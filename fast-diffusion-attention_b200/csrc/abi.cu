@@ -7,6 +7,7 @@
 namespace fda {
 
 size_t bwd_workspace_bytes(const FdaProblem& p);  // bwd_sm100.cu
+size_t fwd_workspace_bytes(const FdaProblem& p);  // fwd_sm100.cu
 
 namespace {
 
@@ -31,8 +32,8 @@ int check_problem(const FdaProblem& p, bool backward) {
 extern "C" {
 
 size_t fda_fwd_workspace_bytes(const FdaProblem* p) {
-  (void)p;
-  return 256;  // scheduler words; the forward keeps no other scratch
+  if (!p) return 0;
+  return fda::fwd_workspace_bytes(*p);
 }
 
 size_t fda_bwd_workspace_bytes(const FdaProblem* p) {

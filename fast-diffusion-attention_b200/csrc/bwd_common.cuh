@@ -9,6 +9,7 @@
 #include "host_util.h"
 #include "ptx.cuh"
 #include "sched.cuh"
+#include "varlen_list.cuh"
 
 #ifndef FDA_SHORT8_KV
 #define FDA_SHORT8_KV 4   // eighths of a (sample, head)'s items that count as short: dK/dV-stationary kernels
@@ -49,6 +50,7 @@ struct BwdParams {
   float* dq_acc;     // single-pass backward: fp32 dQ accumulator, [heads][acc_tiles][head dim][64 queries]
   int acc_tiles;     // 64-row accumulator tiles per query head
   int64_t acc_floats;   // size of the accumulator
+  VarlenList vl;     // packed batches: samples longest first with running 128-row tile counts (base == nullptr otherwise)
   int wide_store;      // dq/dk/dv rows allow 32-byte stores
   float scale_log2, softcap_pre, softmax_scale;
 };
@@ -160,13 +162,24 @@ __device__ __forceinline__ KvItem decode_kv_item(const BwdParams& p, int idx) {
   // stay in L2. Inside a head: clean key tiles first, early ones first (they are seen by the most queries), then
   // the noisy key tiles (one block of queries each) as filler.
   KvItem it;
-  const int per_bh = 2 * p.tiles_per_half;
-  int bh, rem;
-  two_phase_order(idx, per_bh, p.n_long_kv, p.batch * p.heads_k, bh, rem);
-  it.kh = rem < p.tiles_per_half ? 1 : 0;
-  const int kt = rem < p.tiles_per_half ? rem : rem - p.tiles_per_half;
-  it.b = bh / p.heads_k;
-  it.hk = bh - it.b * p.heads_k;
+  int rem, tiles;
+  if (p.vl.base != nullptr) {
+    // packed batch: exactly the key tiles that exist, longest sample first, head after head inside a sample
+    const VarlenPos pos = varlen_locate(p.vl, idx, 2 * p.heads_k);
+    tiles = pos.units;
+    it.b = pos.b;
+    it.hk = pos.rem / (2 * tiles);
+    rem = pos.rem - it.hk * (2 * tiles);
+  } else {
+    const int per_bh = 2 * p.tiles_per_half;
+    int bh;
+    two_phase_order(idx, per_bh, p.n_long_kv, p.batch * p.heads_k, bh, rem);
+    tiles = p.tiles_per_half;
+    it.b = bh / p.heads_k;
+    it.hk = bh - it.b * p.heads_k;
+  }
+  it.kh = rem < tiles ? 1 : 0;
+  const int kt = rem < tiles ? rem : rem - tiles;
   const Sample sm = sample_of(p, it.b);
   it.n = sm.n;
   it.row0 = sm.row0;
@@ -203,6 +216,19 @@ __device__ __forceinline__ KvSpans make_kv_spans(const KvItem& it, int bs) {
 constexpr int kSub = 64;
 constexpr int kSubCols = kSub / kCmpWG;  // 16 query columns per compute warpgroup
 // with no visible row is skipped. All roles walk this sequence identically.
+// Number of key-tile items of a launch: known to the host for the batched layout, read from the work list otherwise.
+__device__ __forceinline__ int kv_item_count(const BwdParams& p) {
+  return (p.vl.base != nullptr ? p.vl.base[0] : p.tiles_per_half * p.batch) * 2 * p.heads_k;
+}
+
+// Host side: the number of items (128-row tiles x 2 halves x heads) a launch has at most; exact for the batched
+// layout, an upper bound for packed batches (whose real count only the device knows).
+inline int bwd_item_bound(const BwdParams& p, int heads) {
+  if (p.vl.base == nullptr) return p.tiles_per_half * 2 * heads * p.batch;
+  const int64_t bound = (static_cast<int64_t>(p.total) / (2 * kTile) + p.batch) * 2 * heads;
+  return bound > (1 << 30) ? (1 << 30) : static_cast<int>(bound);
+}
+
 struct SubStep {
   int h, qh, sa, sb, cls;
 };

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
   const uint32_t tmem = *tmem_slot;
   const int bs = p.block_size;
   const int group = p.heads / p.heads_k;
-  const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+  const int total_items = kv_item_count(p);
 
   if (warp >= kEpiWarp0) {
     // ------------------------------------------------------------------------------------- dQ drain + dK/dV epilogue
@@ -633,7 +633,7 @@ int launch_fused_instance(const BwdParams& p, int sm_count, unsigned stages, cud
     const int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
     FDA_CUDA_TRY(cudaMemsetAsync(p.dq_acc, 0, static_cast<size_t>(p.heads) * p.acc_tiles * 64 * kHeadDim * 4, stream));
-    const int items = p.tiles_per_half * 2 * p.heads_k * p.batch;
+    const int items = bwd_item_bound(p, p.heads_k);
     const int grid = items < sm_count ? items : sm_count;
     kernel<<<grid, kDkdvThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());

@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_dkdv_kernel(const __grid_
   const uint32_t tmem = *tmem_slot;
   const int bs = p.block_size;
   const int group = p.heads / p.heads_k;
-  const int total_items = p.tiles_per_half * 2 * p.heads_k * p.batch * Cfg::kPasses;
+  const int total_items = kv_item_count(p) * Cfg::kPasses;
 
   // Calls fn(SubStep) for every non-skipped sub-step of the item, in order; stops early when fn returns false.
   auto for_each_substep = [&](const KvItem& it, const QueryPlan& plan, const KvSpans& spans, auto&& fn) -> bool {
@@ -498,19 +498,30 @@ struct QItem {
 __device__ __forceinline__ QItem decode_q_item(const BwdParams& p, int idx) {
   // (sample, head)-major for L2 reuse of K / V; inside a head late query tiles first (they see the most keys).
   QItem it;
-  const int per_bh = 2 * p.tiles_per_half;
-  int bh, rem;
-  two_phase_order(idx, per_bh, p.n_long_q, p.batch * p.heads, bh, rem);
+  int rem, tiles;
+  if (p.vl.base != nullptr) {
+    // packed batch: exactly the query tiles that exist, longest sample first, head after head inside a sample
+    const VarlenPos pos = varlen_locate(p.vl, idx, 2 * p.heads);
+    tiles = pos.units;
+    it.b = pos.b;
+    it.h = pos.rem / (2 * tiles);
+    rem = pos.rem - it.h * (2 * tiles);
+  } else {
+    const int per_bh = 2 * p.tiles_per_half;
+    int bh;
+    two_phase_order(idx, per_bh, p.n_long_q, p.batch * p.heads, bh, rem);
+    tiles = p.tiles_per_half;
+    it.b = bh / p.heads;
+    it.h = bh - it.b * p.heads;
+  }
   it.qh = rem & 1;
   const int t_rev = rem >> 1;
-  it.b = bh / p.heads;
-  it.h = bh - it.b * p.heads;
   it.hk = it.h / (p.heads / p.heads_k);
   const Sample sm = sample_of(p, it.b);
   it.n = sm.n;
   it.row0 = sm.row0;
   it.bcoord = sm.bcoord;
-  it.qa = (p.tiles_per_half - 1 - t_rev) * kTile;
+  it.qa = (tiles - 1 - t_rev) * kTile;
   it.valid = it.qa < it.n;
   it.qb = imin(it.qa + kTile, it.n);
   return it;
@@ -605,7 +616,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_dq_kernel(const __grid_con
   ptx::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const int bs = p.block_size;
-  const int total_items = p.tiles_per_half * 2 * p.heads * p.batch;
+  const int total_items = (p.vl.base != nullptr ? p.vl.base[0] : p.tiles_per_half * p.batch) * 2 * p.heads;
 
   // Whole warpgroups: four of compute warps, one of the TMA warp, the two MMA warps and an idle warp. The fifth
   // hands registers to the other four. The counts are set inside the role branches, so that the compiler never
@@ -880,7 +891,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     static PerDeviceFlags smem_set;
     int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
-    const int items = p.tiles_per_half * 2 * p.heads_k * p.batch * Cfg::kPasses;
+    const int items = bwd_item_bound(p, p.heads_k) * Cfg::kPasses;
     const int grid = items < sm_count ? items : sm_count;
     kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
@@ -891,7 +902,7 @@ int launch_bwd_instance(const BwdParams& p, int sm_count, unsigned stages, cudaS
     static PerDeviceFlags smem_set;
     int rc = set_dynamic_smem(kernel, Cfg::kSmemBytes, smem_set);
     if (rc) return rc;
-    const int items = p.tiles_per_half * 2 * p.heads * p.batch;
+    const int items = bwd_item_bound(p, p.heads);
     const int grid = items < sm_count ? items : sm_count;
     kernel<<<grid, kBwdThreads, Cfg::kSmemBytes, stream>>>(p);
     FDA_CUDA_TRY(cudaGetLastError());
@@ -927,7 +938,8 @@ bool bwd_single_pass(const FdaProblem& pr) { return pr.deterministic == 0 && pr.
 size_t bwd_split_workspace_bytes(const FdaProblem& pr) {
   const int64_t n_pad = round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile);
   const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * n_pad * 4, 256);
-  return static_cast<size_t>(2 * one + 256);
+  // ... and for packed batches the work list (samples longest first, running tile counts)
+  return static_cast<size_t>(2 * one + 256) + (pr.cu_seqlens != nullptr ? varlen_list_bytes(pr.batch) : 0);
 }
 
 // The single-pass backward keeps its fp32 dQ accumulator behind that.
@@ -1034,11 +1046,22 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   const bool single_pass = bwd_single_pass(pr) && (stage_mask & FDA_BWD_FORCE_SPLIT) == 0;
   if (single_pass) {
     if (a.workspace_bytes < bwd_workspace_bytes(pr)) return FDA_ERR_WORKSPACE;
-    p.dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + 2 * one + 256);
+    p.dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_split_workspace_bytes(pr));
     p.acc_tiles = static_cast<int>(bwd_fused_acc_tiles(pr));
     p.acc_floats = static_cast<int64_t>(bwd_fused_acc_bytes(pr) / 4);
   }
   if (stage_mask & 6u) FDA_CUDA_TRY(cudaMemsetAsync(p.ticket_kv, 0, 256, stream));
+  if (varlen) {
+    // the work list of the persistent kernels is built on the device (no host synchronisation); every stage call
+    // rebuilds it, so stages may be launched one by one
+    int* list = reinterpret_cast<int*>(static_cast<uint8_t*>(a.workspace) + 2 * one + 256);
+    if (stage_mask & 6u) {
+      rc = launch_varlen_prepare(pr.cu_seqlens, pr.batch, kTile, list, stream);
+      if (rc) return rc;
+    }
+    p.vl.base = list;
+    p.vl.batch = pr.batch;
+  }
   const bool softcap = pr.softcap > 0.f;
   p.softmax_scale = pr.softmax_scale;
   if (softcap) {

@@ -25,6 +25,7 @@
 #include "host_util.h"
 #include "ptx.cuh"
 #include "sched.cuh"
+#include "varlen_list.cuh"
 
 
 #ifndef FDA_SHORT8_FWD
@@ -52,7 +53,8 @@ struct FwdParams {
   int batch, seqlen, total, heads, heads_k, head_dim, block_size;
   int items_per_half;  // ceil(max n / rows per item)
   int n_long;          // of the 2 * items_per_half items of a (sample, head): how many count as long
-  int total_items;
+  int total_items;     // batched layout; packed batches read the count from the work list
+  VarlenList vl;       // packed batches: samples longest first with running item counts (base == nullptr otherwise)
   int* ticket;         // global work counter, zeroed before the launch
   int wide_store;      // rows of out allow 32-byte stores
   const float* q_descale;  // FP8 only: (batch, heads_k) factors, element strides below; nullptr = 1
@@ -76,15 +78,27 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int idx) {
   // (sample, head)-major so that the CTAs running at the same time share the K/V of a few heads in L2; inside a
   // head the items with the most key tiles (late query rows) come first.
   Item it;
-  const int per_bh = 2 * p.items_per_half;
-  int bh, rem;
-  two_phase_order(idx, per_bh, p.n_long, p.batch * p.heads, bh, rem);
+  int rem, items_per_half;
+  if (p.vl.base != nullptr) {
+    // packed batch: the work list holds exactly the items that exist, longest sample first; inside a sample the
+    // heads follow each other, inside a head the items with the most key tiles come first
+    const VarlenPos pos = varlen_locate(p.vl, idx, 2 * p.heads);
+    items_per_half = pos.units;
+    it.b = pos.b;
+    it.h = pos.rem / (2 * pos.units);
+    rem = pos.rem - it.h * (2 * pos.units);
+  } else {
+    const int per_bh = 2 * p.items_per_half;
+    int bh;
+    two_phase_order(idx, per_bh, p.n_long, p.batch * p.heads, bh, rem);
+    items_per_half = p.items_per_half;
+    it.b = bh / p.heads;
+    it.h = bh - it.b * p.heads;
+  }
   it.qh = rem & 1;
   const int p_rev = rem >> 1;
-  it.b = bh / p.heads;
-  it.h = bh - it.b * p.heads;
   it.hk = it.h / (p.heads / p.heads_k);
-  const int pidx = p.items_per_half - 1 - p_rev;
+  const int pidx = items_per_half - 1 - p_rev;
   if (p.cu_seqlens != nullptr) {
     const int s = p.cu_seqlens[it.b];
     const int e = p.cu_seqlens[it.b + 1];
@@ -198,6 +212,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int total_items = p.vl.base != nullptr ? p.vl.base[0] * 2 * p.heads : p.total_items;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -242,7 +257,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_take(mbox, n_sched, p.ticket, abort_flag);
         if (idx < 0) break;
-        if (idx >= p.total_items) {
+        if (idx >= total_items) {
           sched_publish(mbox, n_sched, idx);
           break;
         }
@@ -338,7 +353,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 
       for (uint32_t n_sched = 0; alive; ++n_sched) {
         const int idx = sched_peek(mbox, n_sched, abort_flag);
-        if (idx < 0 || idx >= p.total_items) break;
+        if (idx < 0 || idx >= total_items) break;
         const Item it = desc[n_sched & 1u].it;
         const KeyPlan plan = desc[n_sched & 1u].plan;
         TileSpans spans[kQTiles];
@@ -411,7 +426,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
     uint8_t* stage_o = sStageO + t * Cfg::kStageOBytes;
     for (uint32_t n_sched = 0; alive; ++n_sched) {
       const int idx = sched_peek(mbox, n_sched, abort_flag);
-      if (idx < 0 || idx >= p.total_items) break;
+      if (idx < 0 || idx >= total_items) break;
       const Item it = desc[n_sched & 1u].it;
       const TileSpans spans = desc[n_sched & 1u].spans[t];
       const KeyPlan plan = desc[n_sched & 1u].plan;
@@ -654,6 +669,11 @@ int dispatch_fwd_fp8(const FwdParams& p, int grid, bool softcap, cudaStream_t st
 
 }  // namespace
 
+size_t fwd_workspace_bytes(const FdaProblem& pr) {
+  // scheduler words, and for packed batches the work list
+  return 256 + (pr.cu_seqlens != nullptr ? varlen_list_bytes(pr.batch) : 0);
+}
+
 int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   const FdaProblem& pr = a.p;
   DeviceInfo info;
@@ -736,12 +756,24 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
     p.lse_scale = pr.softmax_scale;
   }
   if (p.total_items <= 0) return FDA_OK;
-  if (!a.workspace || a.workspace_bytes < 256) return FDA_ERR_WORKSPACE;
+  if (!a.workspace || a.workspace_bytes < fwd_workspace_bytes(pr)) return FDA_ERR_WORKSPACE;
   p.ticket = static_cast<int*>(a.workspace);
   FDA_CUDA_TRY(cudaMemsetAsync(p.ticket, 0, 256, stream));
   int grid = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
   if (grid < 1) grid = 1;
-  if (grid > p.total_items) grid = p.total_items;
+  if (varlen) {
+    // the work list is built on the device from cu_seqlens (no host synchronisation): the host only knows an upper
+    // bound of the number of items, blocks beyond the real number find no work and leave
+    int* list = reinterpret_cast<int*>(static_cast<uint8_t*>(a.workspace) + 256);
+    const int rc = launch_varlen_prepare(pr.cu_seqlens, pr.batch, q_tiles * kBlockM, list, stream);
+    if (rc) return rc;
+    p.vl.base = list;
+    p.vl.batch = pr.batch;
+    const int64_t bound = (static_cast<int64_t>(pr.total) / (2 * q_tiles * kBlockM) + pr.batch) * 2 * pr.heads;
+    if (grid > bound) grid = static_cast<int>(bound);
+  } else if (grid > p.total_items) {
+    grid = p.total_items;
+  }
   const bool bf16 = pr.dtype == FDA_BF16;
   if (fp8) {
     if (d_round == 128) return dispatch_fwd_fp8<128, 2, 6>(p, grid, softcap, stream);
