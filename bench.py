@@ -48,7 +48,8 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the headline workload, from ncu captures (bytes)
-NCU_TRAFFIC_BYTES = {"fwd_kernel": 550.7e6, "bwd_dkdv_kernel": 897.0e6, "bwd_dq_kernel": 677.7e6}
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 549.1e6, "bwd_fused_kernel": 1659.5e6, "bwd_dkdv_kernel": 897.0e6,
+                     "bwd_dq_kernel": 677.7e6}
 
 WORKLOAD = dict(name="C2 bf16 MHA fwd+bwd", batch=8, n=2048, heads=16, heads_k=16, head_dim=128, block_size=256)
 METRIC = "train-step TFLOPS (visible pairs), bf16 d=128"
@@ -606,8 +607,10 @@ def main():
     top = max(range(4), key=lambda j: kernel_ms[j])
     achieved = algorithmic[top] / (kernel_ms[top] * 1e-3) / 1e12
     roofline = dict(bound="tensor", kernel=names[top], achieved=achieved, peak=peaks["tflops_burst"], unit="TFLOP/s",
-                    frac=achieved / peaks["tflops_burst"], traffic=None,
-                    traffic_note="no ncu capture of this kernel's DRAM bytes yet",
+                    frac=achieved / peaks["tflops_burst"],
+                    traffic=(NCU_TRAFFIC_BYTES.get(names[top].split(" ")[0]) if world == 1 else None),
+                    traffic_note="bytes per launch, dram read + write of one ncu capture of this kernel on this workload "
+                                 "(one GPU, whole problem)",
                     peak_source=peaks["source"] + " cuBLAS bf16 burst figure: the stage-by-stage region lasts "
                                                   f"{sum(kernel_ms) * stage_steps:.0f} ms at boost clocks",
                     algorithmic_gflop_per_launch=algorithmic[top] / 1e9,
