@@ -623,16 +623,17 @@ def main():
     if not args.skip_sustained:
         n_long = max(200, int(2200.0 / ms_per_step))
         e_marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        run_step = graph.replay if use_graph else step_public
         with ClockSampler(local_rank) as c_burst:
             barrier()
             e_marks[0].record()
             for _ in range(50):
-                step_public()
+                run_step()
             e_marks[1].record()
             torch.cuda.synchronize()
         with ClockSampler(local_rank) as c_long:
             for _ in range(n_long - 50):
-                step_public()
+                run_step()
             e_marks[2].record()
             barrier()
         burst_ms = max_over_ranks(e_marks[0].elapsed_time(e_marks[1]), dist, world, dev) / 50
