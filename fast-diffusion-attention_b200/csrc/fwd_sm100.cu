@@ -498,11 +498,11 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         // exponentials that follow)
         float mx[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) mx[i] = v[i];
+        for (int i = 0; i < 8; ++i) mx[i] = fmaxf(v[2 * i], v[2 * i + 1]);
 #pragma unroll
-        for (int c = 8; c < kBlockN; c += 8) {
+        for (int c = 16; c < kBlockN; c += 16) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) mx[i] = fmaxf(mx[i], v[c + i]);
+          for (int i = 0; i < 8; ++i) mx[i] = ptx::max3(mx[i], v[c + 2 * i], v[c + 2 * i + 1]);
         }
         const float m_tile = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
                                    fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
@@ -540,13 +540,19 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             pk[c / 4] = ptx::pack_e4m3x4(p0, p1, p2, p3);
           }
         } else {
+          // two elements per FMA and per ADD: the sums run as four pairs of partial sums
+          float sumb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int c = 0; c < kBlockN; c += 2) {
-            const float p0 = ptx::ex2(fmaf(v[c], scale_log2, neg_m));
-            const float p1 = ptx::ex2(fmaf(v[c + 1], scale_log2, neg_m));
-            sum4[(c / 2) & 3] += p0 + p1;
+            float y0, y1;
+            ptx::fma2(y0, y1, v[c], v[c + 1], scale_log2, scale_log2, neg_m, neg_m);
+            const float p0 = ptx::ex2(y0);
+            const float p1 = ptx::ex2(y1);
+            ptx::add2(sum4[(c / 2) & 3], sumb[(c / 2) & 3], sum4[(c / 2) & 3], sumb[(c / 2) & 3], p0, p1);
             pk[c / 2] = ptx::pack2<kType == 0>(p0, p1);
           }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sum4[i] += sumb[i];
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 #pragma unroll
