@@ -43,6 +43,10 @@ struct FusedCfg {
   static constexpr int kSmemBytes = kOffBar + 512;
   // tensor memory: S^T / P^T at 0, dP^T / dQ^T at 128, dK and dV behind
   static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDK = 256, kTmemDV = 256 + kHeadDim;
+  // Head dimension 64 leaves 128 columns behind the accumulators: dQ^T gets them, and the next dP^T no longer waits
+  // for the drain of this step's dQ^T. At 128 all 512 columns are taken and dQ^T overwrites dP^T.
+  static constexpr bool kOwnDq = 256 + 2 * kHeadDim + 128 <= 512;
+  static constexpr int kTmemDQ = kOwnDq ? 256 + 2 * kHeadDim : kTmemDP;
   static_assert(kHeadDim == 64 || kHeadDim == 128, "the single-pass backward covers head dimensions up to 128");
   static_assert(kOffStat % 1024 == 0, "tiles stay 1024-byte aligned for the swizzle");
   static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -116,7 +120,8 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
   uint64_t* ds_full = p_full + 1;              // dS^T in shared memory, dP^T in registers
   uint64_t* s_free = ds_full + 1;              // dV has read P^T: the next S^T may overwrite it
   uint64_t* dq_full = s_free + 1;              // dQ^T complete
-  uint64_t* dp_free = dq_full + 1;             // dQ^T is in the drain warps' registers: the next dP^T may overwrite it
+  uint64_t* dp_free = dq_full + 1;             // dQ^T is in the drain warps' registers: its columns may be overwritten
+                                               // (by the next dP^T, or by the next dQ^T where it has columns of its own)
   uint64_t* ds_free = dp_free + 1;             // dQ^T and dK have read dS^T: the next step may overwrite it
   uint64_t* acc_full = ds_free + 1;
   uint64_t* acc_free = acc_full + 1;
@@ -207,7 +212,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t a[32];
-            ptx::tmem_ld32(tmem + Cfg::kTmemDP + lane_addr + c * 32, a);
+            ptx::tmem_ld32(tmem + Cfg::kTmemDQ + lane_addr + c * 32, a);
             float* stage = reinterpret_cast<float*>(sStage + (quad * 2 + (n_bulk & 1u)) * Cfg::kStageChunk);
             // the bulk reduction that last read this slot (two chunks ago) must have finished reading it
             if (lane == 0) ptx::bulk_wait_group_read<1>();
@@ -332,7 +337,8 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
     // ------------------------------------------------------------------- MMA issuer 1: S^T = K Q^T, dP^T = V dO^T
     // Two threads issue the MMAs of this kernel, so that the barrier waits and commits of one overlap the MMAs of
     // the other. S^T of step g + 1 may overwrite P^T of step g once dV has read it (s_free); dP^T of step g + 1
-    // may overwrite dQ^T of step g once the drain warps hold it (dp_free).
+    // may overwrite dQ^T of step g once the drain warps hold it (dp_free) or, where dQ^T has its own columns, dP^T of
+    // step g once the compute warps hold it (ds_full).
     if (lane == 0) {
       constexpr int kFmt = kBf16 ? 1 : 0;
       const uint32_t idesc_s = ptx::make_idesc(kTile, kTile, kFmt, false, false);
@@ -364,7 +370,7 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           ptx::umma_commit(s_full);
           const uint32_t dslot = g % kDoSlots;
           if (!ptx::mbar_wait(&do_full[dslot], (g / kDoSlots) & 1u, abort_flag, 56)) { alive = false; break; }
-          if (!ptx::mbar_wait(dp_free, (g & 1u) ^ 1u, abort_flag, 58)) { alive = false; break; }
+          if (!ptx::mbar_wait(Cfg::kOwnDq ? ds_full : dp_free, (g & 1u) ^ 1u, abort_flag, 58)) { alive = false; break; }
           ptx::tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
@@ -423,9 +429,14 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
           if (!ptx::mbar_wait(ds_full, g & 1u, abort_flag, 59)) { alive = false; break; }
           ptx::tc_fence_after();
           // dQ^T before dK: its drain (tensor memory -> registers -> global adds) then runs under dK
+          if (Cfg::kOwnDq) {
+            // the drain warps hold dQ^T of the previous step
+            if (!ptx::mbar_wait(dp_free, (g & 1u) ^ 1u, abort_flag, 68)) { alive = false; break; }
+            ptx::tc_fence_after();
+          }
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
-            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDP, kt_lo + kk * (2048 >> 4), ds_mn + kk * (2048 >> 4), kHi, idesc_q, kk > 0);
+            ptx::umma_ss_f16_lh(tmem + Cfg::kTmemDQ, kt_lo + kk * (2048 >> 4), ds_mn + kk * (2048 >> 4), kHi, idesc_q, kk > 0);
           }
           ptx::umma_commit(dq_full);
           // K is read by S^T (complete for every step of this item by now) and by dQ^T: after the last dQ^T the next
