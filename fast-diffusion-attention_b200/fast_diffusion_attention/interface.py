@@ -405,3 +405,131 @@ def diffusion_attn_varlen_func(
         assert max_seqlen_k == max_seqlen_q, "max_seqlen_k must be equal to max_seqlen_q"
     return _apply(q, k, v, cu_seqlens_q, max_seqlen_q, block_size, softmax_scale,
                   (q_descale, k_descale, v_descale), softcap, deterministic, sm_margin, return_attn_probs)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Packed projections. The reference takes q, k and v as separate tensors (interface.py:196-250 there); its own test
+# feeds it views of one projection output (tests/test_diffusion_attn.py:260-266). These entry points take that one
+# tensor, as the callers of an attention layer usually hold it, and hand back ONE gradient tensor of the same layout:
+# the kernels read and write the views in place, so neither direction copies or concatenates anything.
+# ---------------------------------------------------------------------------------------------------------------
+def _split_packed(qkv, num_heads_q, varlen):
+    """Views (q, k, v) of a packed projection. Behind the leading axes ((batch, 2n), or (total,) for packed samples)
+    it is either (3, heads, dim) or (heads_q + 2 heads_k, dim) with `num_heads_q` = heads_q."""
+    lead = 1 if varlen else 2
+    if qkv.dim() == lead + 3:
+        if qkv.shape[lead] != 3:
+            raise ValueError(f"axis {lead} of a packed tensor with {qkv.dim()} dimensions must have size 3")
+        if num_heads_q is not None and num_heads_q != qkv.shape[-2]:
+            raise ValueError("num_heads_q disagrees with the head axis")
+        return qkv.select(lead, 0), qkv.select(lead, 1), qkv.select(lead, 2)
+    if qkv.dim() != lead + 2:
+        raise ValueError(f"a packed tensor has {lead + 3} or {lead + 2} dimensions here, got {qkv.dim()}")
+    if num_heads_q is None:
+        raise ValueError("a packed tensor without a separate axis of size 3 needs num_heads_q")
+    heads_total = qkv.shape[-2]
+    if num_heads_q <= 0 or heads_total <= num_heads_q or (heads_total - num_heads_q) % 2 != 0:
+        raise ValueError("the head axis must hold num_heads_q query heads followed by two equal groups of key and "
+                         "value heads")
+    heads_k = (heads_total - num_heads_q) // 2
+    return (qkv.narrow(-2, 0, num_heads_q), qkv.narrow(-2, num_heads_q, heads_k),
+            qkv.narrow(-2, num_heads_q + heads_k, heads_k))
+
+
+@torch.library.custom_op("fda::_diffusion_attn_backward_packed", mutates_args=("dqkv",), device_types="cuda")
+def _diffusion_attn_backward_packed(
+    dout: torch.Tensor,
+    qkv: torch.Tensor,
+    out: torch.Tensor,
+    softmax_lse: torch.Tensor,
+    dqkv: torch.Tensor,
+    block_size: int,
+    num_heads_q: Optional[int] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    max_seqlen: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+    softcap: float = 0.0,
+    deterministic: bool = False,
+    sm_margin: int = 0,
+) -> None:
+    q, k, v = _split_packed(qkv, num_heads_q, cu_seqlens is not None)
+    dq, dk, dv = _split_packed(dqkv, num_heads_q, cu_seqlens is not None)
+    backward_launch(dout, q, k, v, out, softmax_lse, dq, dk, dv, block_size, cu_seqlens, max_seqlen, softmax_scale,
+                    softcap, deterministic, sm_margin)
+
+
+@torch.library.register_fake("fda::_diffusion_attn_backward_packed")
+def _diffusion_attn_backward_packed_fake(dout, qkv, out, softmax_lse, dqkv, block_size, num_heads_q=None,
+                                         cu_seqlens=None, max_seqlen=None, softmax_scale=None, softcap=0.0,
+                                         deterministic=False, sm_margin=0) -> None:
+    return None
+
+
+class _DiffusionAttentionPacked(torch.autograd.Function):
+    """Autograd node of the packed entry points: saves the packed tensor once and returns one packed gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, num_heads_q, cu_seqlens, max_seqlen, block_size, softmax_scale, softcap, deterministic,
+                sm_margin):
+        q, k, v = _split_packed(qkv, num_heads_q, cu_seqlens is not None)
+        scale = q.shape[-1] ** (-0.5) if softmax_scale is None else softmax_scale
+        out, lse = _diffusion_attn_forward(q, k, v, block_size, cu_seqlens, max_seqlen, None, None, None, scale,
+                                           softcap, sm_margin)
+        ctx.save_for_backward(*((qkv, out, lse) + ((cu_seqlens,) if cu_seqlens is not None else ())))
+        ctx.packed = cu_seqlens is not None
+        ctx.opts = (num_heads_q, block_size, max_seqlen, scale, softcap, deterministic, sm_margin)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        qkv, out, lse = ctx.saved_tensors[:3]
+        cu_seqlens = ctx.saved_tensors[3] if ctx.packed else None
+        num_heads_q, block_size, max_seqlen, scale, softcap, deterministic, sm_margin = ctx.opts
+        assert qkv.dtype in (torch.float16, torch.bfloat16), "The backward pass only supports fp16 and bf16"
+        dqkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=qkv.device)
+        _diffusion_attn_backward_packed(dout, qkv, out, lse, dqkv, block_size, num_heads_q, cu_seqlens, max_seqlen,
+                                        scale, softcap, deterministic, sm_margin)
+        return (dqkv,) + (None,) * 8
+
+
+def diffusion_attn_qkvpacked_func(
+    qkv,
+    block_size,
+    num_heads_q=None,
+    softmax_scale=None,
+    softcap=0.0,
+    deterministic=False,
+    sm_margin=0,
+    return_attn_probs=False,
+):
+    """diffusion_attn_func on one packed projection.
+
+    Arguments:
+        qkv: (batch_size, 2n, 3, nheads, headdim), or, for grouped-query attention,
+            (batch_size, 2n, nheads + 2 nheads_k, headdim) with `num_heads_q` = nheads: query heads first, then the
+            key heads, then the value heads. FP16 or BF16; the innermost dimension contiguous.
+        Other arguments as in diffusion_attn_func.
+    Returns out (batch_size, 2n, nheads, headdim), or (out, lse). The gradient of qkv is one tensor of qkv's shape.
+    """
+    out, lse = _DiffusionAttentionPacked.apply(qkv, num_heads_q, None, None, block_size, softmax_scale, softcap,
+                                               deterministic, sm_margin)
+    return (out, lse) if return_attn_probs else out
+
+
+def diffusion_attn_varlen_qkvpacked_func(
+    qkv,
+    cu_seqlens,
+    max_seqlen,
+    block_size,
+    num_heads_q=None,
+    softmax_scale=None,
+    softcap=0.0,
+    deterministic=False,
+    sm_margin=0,
+    return_attn_probs=False,
+):
+    """diffusion_attn_varlen_func on one packed projection: qkv is (total, 3, nheads, headdim) or
+    (total, nheads + 2 nheads_k, headdim) with `num_heads_q`; cu_seqlens and max_seqlen as there."""
+    out, lse = _DiffusionAttentionPacked.apply(qkv, num_heads_q, cu_seqlens, max_seqlen, block_size, softmax_scale,
+                                               softcap, deterministic, sm_margin)
+    return (out, lse) if return_attn_probs else out
