@@ -138,8 +138,9 @@ __device__ __forceinline__ void softmax_backward_cols(const uint32_t* s, const u
       const float l2 = kPerColumn ? lse2_col[col] : lse2_row;
       const float dl = kPerColumn ? delta_col[col] : delta_row;
       float pr = ptx::ex2(fmaf(x, scale_log2, -l2));
-      float d = pr * (__uint_as_float(dp[col]) - dl);
-      if (kSoftcap) d *= dt;
+      // the derivative of the cap goes onto P first: the single-pass backward computes P (1 - tanh^2) in the first
+      // half of its arithmetic and meets dP only in the second, and both forms round alike
+      float d = (kSoftcap ? pr * dt : pr) * (__uint_as_float(dp[col]) - dl);
       if (kMasked && (col < lo || col >= hi)) {
         pr = 0.f;
         d = 0.f;

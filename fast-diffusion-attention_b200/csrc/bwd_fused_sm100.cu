@@ -21,6 +21,8 @@
 // cp.reduce.async.bulk from shared memory) and converts afterwards (flash_bwd_postprocess_kernel.h:160-264).
 // The order of the adds depends on scheduling, so this path serves deterministic == 0 only; the deterministic
 // backward keeps the two-kernel split (dK/dV kernel + dQ kernel), which has no cross-CTA reduction.
+#include <type_traits>
+
 #include "bwd_common.cuh"
 
 
@@ -492,43 +494,46 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
         // visible query columns of this thread's key, relative to its first column of the step
         const int lo = ((hdr0 & 4) ? same_lo : cross_lo) - (hdr1 + wg * kCols);
         const int hi = ((hdr0 & 4) ? same_hi : cross_hi) - (hdr1 + wg * kCols);
-        if constexpr (!kSoftcap) {
-          float pr[kCols];   // the step's probabilities of this thread, kept from the first half of the arithmetic
+        {
+          // First half, once S^T is complete: P^T (16-bit, back to tensor memory for dV) and, kept in registers, the
+          // factor of the second half: P, or with the score cap P (1 - tanh^2).
+          float pr[kCols];
           if (!ptx::mbar_wait(s_full, par, abort_flag, 61)) { alive = false; break; }
           ptx::tc_fence_after();
           {
-            uint32_t sv[kCols];
+            uint32_t sv[kCols], pk[kCols / 2];
             ptx::tmem_ld16(s_t, sv);
             ptx::tmem_ld16(s_t + 16, sv + 16);
             ptx::tmem_wait_ld();
             const float4* l2v = reinterpret_cast<const float4*>(stats);
-            if (!masked) {
-#pragma unroll
-              for (int i = 0; i < kCols / 4; ++i) {
-                const float4 l2 = l2v[i];
-                pr[4 * i] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i]), p.scale_log2, -l2.x));
-                pr[4 * i + 1] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 1]), p.scale_log2, -l2.y));
-                pr[4 * i + 2] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 2]), p.scale_log2, -l2.z));
-                pr[4 * i + 3] = ptx::ex2(fmaf(__uint_as_float(sv[4 * i + 3]), p.scale_log2, -l2.w));
-              }
-            } else {
+            // the fully visible tile (the common one) carries no per-element compare
+            auto first_half = [&](auto masked_tag) {
+              constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
               for (int i = 0; i < kCols / 4; ++i) {
                 const float4 l2 = l2v[i];
                 const float l2a[4] = {l2.x, l2.y, l2.z, l2.w};
+                float pv[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                   const int c = 4 * i + j;
-                  const float v = ptx::ex2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -l2a[j]));
-                  pr[c] = (c < lo || c >= hi) ? 0.f : v;
+                  float x = __uint_as_float(sv[c]);
+                  float dt = 1.f;
+                  if (kSoftcap) {
+                    x = ptx::tanh_fast(x * p.softcap_pre);
+                    dt = 1.f - x * x;
+                  }
+                  float v = ptx::ex2(fmaf(x, p.scale_log2, -l2a[j]));
+                  if (kMasked && (c < lo || c >= hi)) v = 0.f;
+                  pv[j] = v;
+                  pr[c] = kSoftcap ? v * dt : v;
                 }
+                pk[2 * i] = ptx::pack2<kBf16>(pv[0], pv[1]);
+                pk[2 * i + 1] = ptx::pack2<kBf16>(pv[2], pv[3]);
               }
-            }
-          }
-          {
-            uint32_t pk[kCols / 2];
-#pragma unroll
-            for (int c = 0; c < kCols / 2; ++c) pk[c] = ptx::pack2<kBf16>(pr[2 * c], pr[2 * c + 1]);
+            };
+            if (masked) first_half(std::true_type{});
+            else first_half(std::false_type{});
             // a warp overwrites only columns it has itself already loaded: the 16-bit P^T of its 32 queries goes to
             // the first 16 of its own 32 columns
             ptx::tmem_st16(s_t, pk);
@@ -561,32 +566,6 @@ __global__ void __launch_bounds__(kDkdvThreads, 1) bwd_fused_kernel(const __grid
               ptx::st_shared_v4(ds_row + (((ds_piece0 + i) ^ (row & 7)) << 4), pk[0], pk[1], pk[2], pk[3]);
             }
           }
-        } else {
-          // with the cap the second half needs the tanh of the first: both halves run per 16 columns once S^T and
-          // dP^T are complete, and nothing is carried across
-          if (!ptx::mbar_wait(s_full, par, abort_flag, 61)) { alive = false; break; }
-          if (!ptx::mbar_wait(dp_full, par, abort_flag, 65)) { alive = false; break; }
-          if (!ptx::mbar_wait(ds_free, par ^ 1u, abort_flag, 66)) { alive = false; break; }
-          ptx::tc_fence_after();
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t sv[16], dpv[16];
-            ptx::tmem_ld16(s_t + half * 16, sv);
-            ptx::tmem_ld16(dp_t + half * 16, dpv);
-            ptx::tmem_wait_ld();
-            uint32_t pk_p[8], pk_ds[8];
-            softmax_backward_cols<16, kBf16, true, true, true, true>(sv, dpv, stats + half * 16, stats + kTile + half * 16,
-                                                                     0.f, 0.f, p.scale_log2, p.softcap_pre,
-                                                                     masked ? lo - half * 16 : -(1 << 30),
-                                                                     masked ? hi - half * 16 : (1 << 30), pk_p, pk_ds);
-            ptx::tmem_st8(s_t + half * 8, pk_p);
-            const int piece = ds_piece0 + 2 * half;
-            ptx::st_shared_v4(ds_row + ((piece ^ (row & 7)) << 4), pk_ds[0], pk_ds[1], pk_ds[2], pk_ds[3]);
-            ptx::st_shared_v4(ds_row + (((piece + 1) ^ (row & 7)) << 4), pk_ds[4], pk_ds[5], pk_ds[6], pk_ds[7]);
-          }
-          ptx::tmem_wait_st();
-          ptx::tc_fence_before();
-          ptx::mbar_arrive_warp(p_full);
         }
         if (threadIdx.x == 0) {
           dq_desc[2 * par] = hdr0 & ~6;
