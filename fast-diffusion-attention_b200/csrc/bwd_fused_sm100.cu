@@ -3,11 +3,13 @@
 // One CTA per (128-key tile, KV head, sample, half), persistent. K and V stay in shared memory; the visible
 // 128-row query tiles of every query head of the group stream through. Per (key tile, query tile) step:
 //   S^T  = K Q^T                        keys on tensor-memory lanes, 128 query columns
-//   P^T  = exp2(S^T c - LSE2)           compute warps; written back over S^T as 16-bit
+//   P^T  = exp2(S^T c - LSE2)           compute warps; written back over S^T as 16-bit (with a score cap: of
+//                                       cap * tanh(S^T / cap), and the factor kept for dS^T is P^T (1 - tanh^2))
 //   dP^T = V dO^T                       a second 128-column buffer
 //   dS^T = P^T (dP^T - delta)           compute warps; to shared memory as 16-bit, [keys][queries]
 //   dV  += P^T dO, dK += dS^T Q         accumulators in tensor memory for the whole key tile
 //   dQ^T = K^T dS^T                     head dim on lanes, 128 query columns, written over the consumed dP^T buffer
+//                                       (head dim 64 leaves room for columns of its own)
 // The two halves of the arithmetic hang on different products, so they overlap different MMAs: P^T is computed while
 // dP^T (and the tail of the previous step) runs, dS^T while dV runs. The partial dQ^T of a step is added into an fp32
 // accumulator in global memory: the drain warps move it from tensor memory through a small shared-memory staging
