@@ -1030,14 +1030,6 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   p.block_size = pr.block_size;
   p.n_pad = static_cast<int>(round_up64(pr.seqlen / 2 > 0 ? pr.seqlen / 2 : 1, kTile));
   p.tiles_per_half = p.n_pad / kTile;
-  {
-    // dK/dV: the noisy key tiles (the second half of the ranks) are short; dQ: the shortest eighth (fractions
-    // found by measurement on the benchmark shape)
-    const int per_bh = 2 * p.tiles_per_half;
-    p.n_long_kv = per_bh - (FDA_SHORT8_KV * per_bh) / 8;
-    if (p.n_long_kv < 1) p.n_long_kv = 1;
-    p.n_long_q = per_bh - (FDA_SHORT8_Q * per_bh) / 8;
-  }
   const int64_t one = round_up64(static_cast<int64_t>(pr.batch) * pr.heads * 2 * p.n_pad * 4, 256);
   p.delta_pad = static_cast<float*>(a.workspace);
   p.lse2_pad = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + one);
@@ -1073,6 +1065,13 @@ int launch_bwd(const FdaBwdArgs& a, cudaStream_t stream, unsigned stage_mask) {
   }
   int sm_count = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
   if (sm_count < 1) sm_count = 1;
+  {
+    // dK/dV: the noisy key tiles (the second half of the ranks) are short; dQ: the shortest eighth (fractions
+    // found by measurement on the benchmark shape); few items per CTA: rank for rank over all of them
+    const int per_bh = 2 * p.tiles_per_half;
+    p.n_long_kv = order_n_long(per_bh, FDA_SHORT8_KV, static_cast<long long>(per_bh) * pr.batch * pr.heads_k, sm_count);
+    p.n_long_q = order_n_long(per_bh, FDA_SHORT8_Q, static_cast<long long>(per_bh) * pr.batch * pr.heads, sm_count);
+  }
   const bool bf16 = pr.dtype == FDA_BF16;
 
   if (stage_mask & 1u) {

@@ -747,10 +747,6 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   const int max_n = pr.seqlen / 2;
   p.items_per_half = ceil_div(max_n, q_tiles * kBlockM);
   p.total_items = p.items_per_half * 2 * pr.heads * pr.batch;
-  {
-    const int per_bh = 2 * p.items_per_half;
-    p.n_long = per_bh - (FDA_SHORT8_FWD * per_bh) / 8;   // the shortest eighths run at the end
-  }
   const bool softcap = pr.softcap > 0.f;
   if (softcap) {
     p.scale_log2 = pr.softcap * kLog2e;
@@ -767,6 +763,8 @@ int launch_fwd(const FdaFwdArgs& a, cudaStream_t stream) {
   FDA_CUDA_TRY(cudaMemsetAsync(p.ticket, 0, 256, stream));
   int grid = info.sm_count - (pr.sm_margin > 0 ? pr.sm_margin : 0);
   if (grid < 1) grid = 1;
+  // the shortest eighths of every (sample, head) run at the end; few items per CTA: rank for rank over all of them
+  p.n_long = order_n_long(2 * p.items_per_half, FDA_SHORT8_FWD, p.total_items, grid);
   if (varlen) {
     // the work list is built on the device from cu_seqlens (no host synchronisation): the host only knows an upper
     // bound of the number of items, blocks beyond the real number find no work and leave

@@ -33,8 +33,17 @@ __device__ __forceinline__ void sched_init(SchedMailbox* m, int consumer_arrival
 // groups follow each other (group-major), so that the CTAs running at the same time share a group's tiles in L2;
 // but the short items of ALL groups come after the long items of all groups: the kernel then ends on short
 // items, and the CTAs finish within one short item of each other instead of one long one.
+//
+// A launch with only a few items per CTA (n_long < 0) drops the grouping: rank for rank over all groups, so that
+// every group's longest items start first. (Group-major, the CTAs would reach the last groups' longest items only
+// after a full round, and the launch would end one long item later than it has to.)
 __device__ __forceinline__ void two_phase_order(int idx, int per_group, int n_long, int n_groups, int& group,
                                                 int& rank) {
+  if (n_long < 0) {
+    rank = idx / n_groups;
+    group = idx - rank * n_groups;
+    return;
+  }
   const int long_total = n_long * n_groups;
   if (idx < long_total) {
     group = idx / n_long;
@@ -45,6 +54,19 @@ __device__ __forceinline__ void two_phase_order(int idx, int per_group, int n_lo
     group = j / n_short;
     rank = n_long + (j - group * n_short);
   }
+}
+
+// Host side: the n_long of a launch. `short8` eighths of a group's items count as short. Launches with more than
+// two and at most FDA_RANK_MAJOR_ITEMS_PER_CTA items per CTA use the rank-major order (-1): with more items the
+// tail matters less than sharing a group's tiles in L2, and with fewer than two rounds a CTA that starts on a short
+// item of an early group and then takes a long one of a late group does better than longest-first.
+#ifndef FDA_RANK_MAJOR_ITEMS_PER_CTA
+#define FDA_RANK_MAJOR_ITEMS_PER_CTA 8
+#endif
+inline int order_n_long(int per_group, int short8, long long total_items, int ctas) {
+  if (total_items > 2LL * ctas && total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
+  const int n_long = per_group - (short8 * per_group) / 8;
+  return n_long < 1 ? 1 : n_long;
 }
 
 // Producer side, one thread, in two halves so that the producer can leave a description of the item in shared
