@@ -56,15 +56,18 @@ __device__ __forceinline__ void two_phase_order(int idx, int per_group, int n_lo
   }
 }
 
-// Host side: the n_long of a launch. `short8` eighths of a group's items count as short. Launches with more than
-// two and at most FDA_RANK_MAJOR_ITEMS_PER_CTA items per CTA use the rank-major order (-1): with more items the
-// tail matters less than sharing a group's tiles in L2, and with fewer than two rounds a CTA that starts on a short
-// item of an early group and then takes a long one of a late group does better than longest-first.
+// Host side: the n_long of a launch. `short8` eighths of a group's items count as short. Launches with at most
+// FDA_RANK_MAJOR_ITEMS_PER_CTA items per CTA use the rank-major order (-1); with more items the tail matters less
+// than sharing a group's tiles in L2.
 #ifndef FDA_RANK_MAJOR_ITEMS_PER_CTA
 #define FDA_RANK_MAJOR_ITEMS_PER_CTA 8
 #endif
+#ifndef FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA
+#define FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA 0
+#endif
 inline int order_n_long(int per_group, int short8, long long total_items, int ctas) {
-  if (total_items > 2LL * ctas && total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
+  if (total_items > static_cast<long long>(FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA) * ctas &&
+      total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
   const int n_long = per_group - (short8 * per_group) / 8;
   return n_long < 1 ? 1 : n_long;
 }
