@@ -48,7 +48,7 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch on the headline workload, from ncu captures (bytes)
-NCU_TRAFFIC_BYTES = {"fwd_kernel": 549.1e6, "bwd_fused_kernel": 1659.5e6, "bwd_dkdv_kernel": 897.0e6,
+NCU_TRAFFIC_BYTES = {"fwd_kernel": 548.7e6, "bwd_fused_kernel": 1655.3e6, "bwd_dkdv_kernel": 897.0e6,
                      "bwd_dq_kernel": 677.7e6}
 
 WORKLOAD = dict(name="C2 bf16 MHA fwd+bwd", batch=8, n=2048, heads=16, heads_k=16, head_dim=128, block_size=256)
