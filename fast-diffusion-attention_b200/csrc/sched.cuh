@@ -62,12 +62,8 @@ __device__ __forceinline__ void two_phase_order(int idx, int per_group, int n_lo
 #ifndef FDA_RANK_MAJOR_ITEMS_PER_CTA
 #define FDA_RANK_MAJOR_ITEMS_PER_CTA 8
 #endif
-#ifndef FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA
-#define FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA 0
-#endif
 inline int order_n_long(int per_group, int short8, long long total_items, int ctas) {
-  if (total_items > static_cast<long long>(FDA_RANK_MAJOR_MIN_ITEMS_PER_CTA) * ctas &&
-      total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
+  if (total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
   const int n_long = per_group - (short8 * per_group) / 8;
   return n_long < 1 ? 1 : n_long;
 }
