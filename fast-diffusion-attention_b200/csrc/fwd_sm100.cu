@@ -186,6 +186,15 @@ struct FwdConfig {
   static constexpr int kTmemS = 0;                  // S_t at t*128
   static constexpr int kTmemO = 128 * kQTiles;      // O_t at kTmemO + t*kHeadDim
   static_assert(kTmemO + kQTiles * kHeadDim <= 512, "tensor memory budget");
+  // Where columns are left over (head dimensions up to 64) the packed P gets columns of its own instead of
+  // overwriting S, and every query tile gets its own MMA issuer. The next S of a tile is then issued as soon as its
+  // softmax warps have read this one and runs under their arithmetic; with P in place of S it has to wait for the
+  // P V product, and the chain softmax -> P V -> S -> softmax sets the pace. (One issuer for both tiles is held in
+  // the issue of 24 small MMAs per step for longer than a softmax takes.)
+  static constexpr bool kOwnP = kQTiles == 2 && kQTiles * (128 + kHeadDim + kPCols) <= 512;
+  static constexpr int kTmemP = kOwnP ? kTmemO + kQTiles * kHeadDim : kTmemS;   // P_t at kTmemP + t*kPStride
+  static constexpr int kPStride = kOwnP ? kPCols : 128;
+  static constexpr int kIssuers = kOwnP ? kQTiles : 1;
 };
 
 template <int kHeadDim, int kQTiles, int kStages, int kType, bool kSoftcap>
@@ -204,7 +213,10 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
   uint64_t* s_full = kv_empty + kStages;         // kQTiles
   uint64_t* p_full = s_full + kQTiles;           // kQTiles
   uint64_t* o_full = p_full + kQTiles;           // kQTiles
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + kQTiles);
+  uint64_t* s_free = o_full + kQTiles;           // kQTiles; used where P has its own columns: S is in registers
+  uint64_t* p_free = s_free + kQTiles;           // kQTiles; likewise: P V has read P (and updated O)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(p_free + kQTiles);
+  static_assert((2 + 2 * kStages + 5 * kQTiles) * 8 + 8 <= 256, "barrier area");
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   SchedMailbox* mbox = reinterpret_cast<SchedMailbox*>(reinterpret_cast<uint8_t*>(bars) + 256);
   ItemDesc* desc = reinterpret_cast<ItemDesc*>(reinterpret_cast<uint8_t*>(bars) + 512);  // two slots
@@ -216,17 +228,19 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    sched_init(mbox, 4 * kQTiles + 1);
+    sched_init(mbox, 4 * kQTiles + Cfg::kIssuers);
     ptx::mbar_init(q_full, 1);
-    ptx::mbar_init(q_empty, 1);
+    ptx::mbar_init(q_empty, Cfg::kIssuers);
     for (int i = 0; i < kStages; ++i) {
       ptx::mbar_init(&kv_full[i], 1);
-      ptx::mbar_init(&kv_empty[i], 1);
+      ptx::mbar_init(&kv_empty[i], Cfg::kIssuers);   // every issuer lets go of the tile
     }
     for (int t = 0; t < kQTiles; ++t) {
       ptx::mbar_init(&s_full[t], 1);
       ptx::mbar_init(&p_full[t], 4);  // one arrival per softmax warp
       ptx::mbar_init(&o_full[t], 1);
+      ptx::mbar_init(&s_free[t], 4);
+      ptx::mbar_init(&p_free[t], 1);
     }
     ptx::fence_mbar_init();
   }
@@ -312,7 +326,91 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
       }
       if (*abort_flag) __nanosleep(100000);  // let copies in flight land before the CTA exits
     }
-  } else if (warp == Cfg::kMmaWarp) {
+  } else if (Cfg::kOwnP && warp >= Cfg::kMmaWarp && warp < Cfg::kMmaWarp + Cfg::kIssuers) {
+    // ------------------------------------------------------------------------------- MMA issuer of one query tile
+    // P has its own columns: S of step s is issued as soon as the softmax warps hold S of step s - 1 (s_free), P V of
+    // step s - 1 when they have written P (p_full). Every issuer waits for every K / V tile and lets go of it, also
+    // where its own query tile skips the step: an issuer can then never be a whole ring ahead of the other.
+    if (lane == 0) {
+      const int t = warp - Cfg::kMmaWarp;
+      constexpr int kFmt = kType == 0 ? 1 : 0;
+      const uint32_t idesc_s = ptx::make_idesc(kBlockM, kBlockN, kFmt, false, false);
+      const uint32_t idesc_o = ptx::make_idesc(kBlockM, kHeadDim, kFmt, false, true);
+      constexpr uint32_t kDescHi = ptx::smem_desc_hi(1024);
+      const uint32_t q_lo = ptx::smem_desc_lo(ptx::smem_u32(sQ), 16) + t * (Cfg::kTileBytes >> 4);
+      const uint32_t k_lo0 = ptx::smem_desc_lo(ptx::smem_u32(sKV), 16);
+      const uint32_t v_lo0 = ptx::smem_desc_lo(ptx::smem_u32(sKV), Cfg::kPanelBytes);
+      const uint32_t tmem_s_t = tmem + Cfg::kTmemS + t * 128;
+      const uint32_t tmem_p_t = tmem + Cfg::kTmemP + t * Cfg::kPStride;
+      const uint32_t tmem_o_t = tmem + Cfg::kTmemO + t * kHeadDim;
+      uint32_t slot = 0, n_item = 0, cnt_p = 0, cnt_s = 0;
+      bool alive = true;
+      for (uint32_t n_sched = 0; alive; ++n_sched) {
+        const int idx = sched_peek(mbox, n_sched, abort_flag);
+        if (idx < 0 || idx >= total_items) break;
+        const Item it = desc[n_sched & 1u].it;
+        const KeyPlan plan = desc[n_sched & 1u].plan;
+        const TileSpans spans = desc[n_sched & 1u].spans[t];
+        sched_release<false>(mbox, n_sched);
+        if (!it.valid) continue;
+        const int steps = plan.steps();
+        if (!ptx::mbar_wait(q_full, n_item & 1, abort_flag, 21)) { alive = false; break; }
+        bool pend = false, o_acc = false;
+        for (int s = 0; s <= steps && alive; ++s) {
+          const uint32_t slot_k = slot + 2 * s;        // K tile of step s
+          const uint32_t slot_v = slot + 2 * s - 1;    // V tile of step s-1
+          bool vis = false;
+          if (s < steps) {
+            int kh, kt;
+            plan.step(s, kh, kt);
+            vis = spans.classify(kh, kt) != kTileSkip;
+            if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 22)) { alive = false; break; }
+            if (vis) {
+              if (!ptx::mbar_wait(&s_free[t], (cnt_s & 1) ^ 1, abort_flag, 25)) { alive = false; break; }
+              ++cnt_s;
+              ptx::tc_fence_after();
+              const uint32_t b_lo = k_lo0 + (slot_k % kStages) * (Cfg::kTileBytes >> 4);
+#pragma unroll
+              for (int kk = 0; kk < kHeadDim / Cfg::kStepElems; ++kk) {
+                const uint32_t off = ((kk / 4) * Cfg::kPanelBytes + (kk % 4) * 32) >> 4;
+                if (Cfg::kFp8) ptx::umma_ss_f8_lh(tmem_s_t, q_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
+                else ptx::umma_ss_f16_lh(tmem_s_t, q_lo + off, b_lo + off, kDescHi, idesc_s, kk > 0);
+              }
+              ptx::umma_commit(&s_full[t]);
+            }
+            // arrives when this thread's products so far are complete (at once if it issued none on the tile)
+            ptx::umma_commit(&kv_empty[slot_k % kStages]);
+            if (s == steps - 1) ptx::umma_commit(q_empty);   // Q is read by the S products only
+          }
+          if (s > 0) {
+            if (!ptx::mbar_wait(&kv_full[slot_v % kStages], (slot_v / kStages) & 1, abort_flag, 23)) { alive = false; break; }
+            if (pend) {
+              if (!ptx::mbar_wait(&p_full[t], cnt_p & 1, abort_flag, 24)) { alive = false; break; }
+              ++cnt_p;
+              ptx::tc_fence_after();
+              const uint32_t b_lo = v_lo0 + (slot_v % kStages) * (Cfg::kTileBytes >> 4);
+#pragma unroll
+              for (int kk = 0; kk < kBlockN / Cfg::kStepElems; ++kk) {
+                const uint32_t b = b_lo + kk * ((Cfg::kStepElems * 128) >> 4);
+                const uint32_t acc = (o_acc || kk > 0) ? 1u : 0u;
+                if (Cfg::kFp8) ptx::umma_ts_f8_lh(tmem_o_t, tmem_p_t + kk * 8, b, kDescHi, idesc_o, acc);
+                else ptx::umma_ts_f16_lh(tmem_o_t, tmem_p_t + kk * 8, b, kDescHi, idesc_o, acc);
+              }
+              ptx::umma_commit(&p_free[t]);
+              o_acc = true;
+            }
+            ptx::umma_commit(&kv_empty[slot_v % kStages]);
+          }
+          pend = vis;
+        }
+        if (!alive) break;
+        if (steps == 0) ptx::umma_commit(q_empty);
+        if (it.qa + t * kBlockM < it.qb) ptx::umma_commit(&o_full[t]);
+        slot += 2 * steps;
+        ++n_item;
+      }
+    }
+  } else if (!Cfg::kOwnP && warp == Cfg::kMmaWarp) {
     // --------------------------------------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr int kFmt = kType == 0 ? 1 : 0;  // kind::f16: 1 = bf16, 0 = f16; kind::f8f6f4: 0 = e4m3
@@ -421,6 +519,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem + Cfg::kTmemS + t * 128 + lane_addr;
     const uint32_t tmem_o = tmem + Cfg::kTmemO + t * kHeadDim + lane_addr;
+    const uint32_t tmem_p = tmem + Cfg::kTmemP + t * Cfg::kPStride + lane_addr;
     uint32_t cnt_s = 0, cnt_o = 0;
     bool alive = true;
     uint8_t* stage_o = sStageO + t * Cfg::kStageOBytes;
@@ -478,6 +577,21 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           for (int c = 0; c < kBlockN / 32; ++c) ptx::tmem_ld32(tmem_s + c * 32, u + c * 32);
           ptx::tmem_wait_ld();
         }
+        // cnt_s - 1 tiles came before this one. With P in its own columns: S may be overwritten from here on, and
+        // the P V product of the previous tile must have completed before O is rescaled or P is overwritten (with P
+        // in place of S the S product of this tile already followed it through the pipe).
+        bool pv_done = !Cfg::kOwnP;
+        auto wait_pv = [&]() -> bool {
+          if (pv_done) return true;
+          pv_done = true;
+          if (!ptx::mbar_wait(&p_free[t], cnt_s & 1, abort_flag, 33)) return false;
+          ptx::tc_fence_after();
+          return true;
+        };
+        if (Cfg::kOwnP) {
+          ptx::tc_fence_before();
+          ptx::mbar_arrive_warp(&s_free[t]);
+        }
         if (kSoftcap) {
 #pragma unroll
           for (int c = 0; c < kBlockN; ++c) v[c] = ptx::tanh_fast(v[c] * softcap_pre);
@@ -512,6 +626,7 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
         if (__any_sync(0xffffffffu, need)) {
           const float factor = need ? ptx::ex2((m_run - m_new) * scale_log2) : 1.f;
           if (o_started) {
+            if (!wait_pv()) { alive = false; break; }
 #pragma unroll
             for (int c = 0; c < kHeadDim / 32; ++c) {
               uint32_t o[32];
@@ -555,8 +670,9 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
           for (int i = 0; i < 4; ++i) sum4[i] += sumb[i];
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (!wait_pv()) { alive = false; break; }
 #pragma unroll
-        for (int c = 0; c < Cfg::kPCols / 32; ++c) ptx::tmem_st32(tmem_s + c * 32, pk + c * 32);
+        for (int c = 0; c < Cfg::kPCols / 32; ++c) ptx::tmem_st32(tmem_p + c * 32, pk + c * 32);
         ptx::tmem_wait_st();
         ptx::tc_fence_before();
         ptx::mbar_arrive_warp(&p_full[t]);
