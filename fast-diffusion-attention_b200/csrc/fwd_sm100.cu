@@ -194,6 +194,8 @@ struct FwdConfig {
   static constexpr bool kOwnP = kQTiles == 2 && kQTiles * (128 + kHeadDim + kPCols) <= 512;
   static constexpr int kTmemP = kOwnP ? kTmemO + kQTiles * kHeadDim : kTmemS;   // P_t at kTmemP + t*kPStride
   static constexpr int kPStride = kOwnP ? kPCols : 128;
+  // (Two issuers with P in place of S, as head dimension 128 would need, are slower than one: 0.38 against 0.31 ms
+  // on the benchmark shape, the two threads' products interleave in the pipe and every one of them takes longer.)
   static constexpr int kIssuers = kOwnP ? kQTiles : 1;
 };
 
@@ -364,9 +366,13 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             int kh, kt;
             plan.step(s, kh, kt);
             vis = spans.classify(kh, kt) != kTileSkip;
-            if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 22)) { alive = false; break; }
+          }
+          // S of step s
+          auto do_s = [&]() -> bool {
+            if (s >= steps) return true;
+            if (!ptx::mbar_wait(&kv_full[slot_k % kStages], (slot_k / kStages) & 1, abort_flag, 22)) return false;
             if (vis) {
-              if (!ptx::mbar_wait(&s_free[t], (cnt_s & 1) ^ 1, abort_flag, 25)) { alive = false; break; }
+              if (!ptx::mbar_wait(&s_free[t], (cnt_s & 1) ^ 1, abort_flag, 25)) return false;
               ++cnt_s;
               ptx::tc_fence_after();
               const uint32_t b_lo = k_lo0 + (slot_k % kStages) * (Cfg::kTileBytes >> 4);
@@ -381,11 +387,14 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
             // arrives when this thread's products so far are complete (at once if it issued none on the tile)
             ptx::umma_commit(&kv_empty[slot_k % kStages]);
             if (s == steps - 1) ptx::umma_commit(q_empty);   // Q is read by the S products only
-          }
-          if (s > 0) {
-            if (!ptx::mbar_wait(&kv_full[slot_v % kStages], (slot_v / kStages) & 1, abort_flag, 23)) { alive = false; break; }
+            return true;
+          };
+          // P V of step s - 1
+          auto do_pv = [&]() -> bool {
+            if (s == 0) return true;
+            if (!ptx::mbar_wait(&kv_full[slot_v % kStages], (slot_v / kStages) & 1, abort_flag, 23)) return false;
             if (pend) {
-              if (!ptx::mbar_wait(&p_full[t], cnt_p & 1, abort_flag, 24)) { alive = false; break; }
+              if (!ptx::mbar_wait(&p_full[t], cnt_p & 1, abort_flag, 24)) return false;
               ++cnt_p;
               ptx::tc_fence_after();
               const uint32_t b_lo = v_lo0 + (slot_v % kStages) * (Cfg::kTileBytes >> 4);
@@ -400,7 +409,10 @@ __global__ void __launch_bounds__(kQTiles == 2 ? 384 : 128 * kQTiles + 64, 1) fw
               o_acc = true;
             }
             ptx::umma_commit(&kv_empty[slot_v % kStages]);
-          }
+            return true;
+          };
+          // S first: it only needs the previous S to have been read
+          if (!do_s() || !do_pv()) { alive = false; break; }
           pend = vis;
         }
         if (!alive) break;
