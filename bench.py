@@ -289,6 +289,9 @@ def other_config_legs(dev, peaks):
             with torch.no_grad():
                 fwd()
 
+        # every leg starts as a burst, like the headline: the legs before it leave the clock lower than boost
+        sync()
+        time.sleep(1.5)
         for _ in range(3):
             step()
         with ClockSampler(dev.index) as clocks:
@@ -359,6 +362,8 @@ def other_config_legs(dev, peaks):
     def fwd8():
         diffusion_attn_func(q8, k8, v8, bs, q_descale=qd, k_descale=kd, v_descale=vd)
 
+    sync()
+    time.sleep(1.5)
     for _ in range(3):
         fwd8()
     with ClockSampler(dev.index) as clocks:
