@@ -165,6 +165,19 @@ int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int
   return c;
 }
 
+int fda_geom_item_order(int idx, int per_group, int n_groups, int short8, int ctas, int32_t* out_group, int32_t* out_rank) {
+  if (per_group < 1 || n_groups < 1 || ctas < 1 || short8 < 0 || short8 > 8 || idx < 0 ||
+      static_cast<long long>(idx) >= static_cast<long long>(per_group) * n_groups || !out_group || !out_rank) {
+    return -1;
+  }
+  const int n_long = fda::order_n_long(per_group, short8, static_cast<long long>(per_group) * n_groups, ctas);
+  int group = 0, rank = 0;
+  fda::two_phase_order(idx, per_group, n_long, n_groups, group, rank);
+  *out_group = group;
+  *out_rank = rank;
+  return 0;
+}
+
 int fda_selftest_wait(long long limit_cycles, void* stream) {
   return fda::launch_selftest_wait(limit_cycles, static_cast<cudaStream_t>(stream));
 }

@@ -165,4 +165,45 @@ FDA_HD QueryPlan make_query_plan(int kh, int k0, int k1, int n, int bs, int bm) 
   return p;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Order in which the persistent kernels take their items
+// ---------------------------------------------------------------------------------------------------------
+// Order of the items. Every group (a sample and head) has `per_group` items ranked longest first. Rank for rank the
+// groups follow each other (group-major), so that the CTAs running at the same time share a group's tiles in L2;
+// but the short items of ALL groups come after the long items of all groups: the kernel then ends on short
+// items, and the CTAs finish within one short item of each other instead of one long one.
+//
+// A launch with only a few items per CTA (n_long < 0) drops the grouping: rank for rank over all groups, so that
+// every group's longest items start first. (Group-major, the CTAs would reach the last groups' longest items only
+// after a full round, and the launch would end one long item later than it has to.)
+FDA_HD void two_phase_order(int idx, int per_group, int n_long, int n_groups, int& group, int& rank) {
+  if (n_long < 0) {
+    rank = idx / n_groups;
+    group = idx - rank * n_groups;
+    return;
+  }
+  const int long_total = n_long * n_groups;
+  if (idx < long_total) {
+    group = idx / n_long;
+    rank = idx - group * n_long;
+  } else {
+    const int j = idx - long_total;
+    const int n_short = per_group - n_long;   // > 0 here, or long_total would cover every index
+    group = j / n_short;
+    rank = n_long + (j - group * n_short);
+  }
+}
+
+// Host side: the n_long of a launch. `short8` eighths of a group's items count as short. Launches with at most
+// FDA_RANK_MAJOR_ITEMS_PER_CTA items per CTA use the rank-major order (-1); with more items the tail matters less
+// than sharing a group's tiles in L2.
+#ifndef FDA_RANK_MAJOR_ITEMS_PER_CTA
+#define FDA_RANK_MAJOR_ITEMS_PER_CTA 8
+#endif
+FDA_HD int order_n_long(int per_group, int short8, long long total_items, int ctas) {
+  if (total_items <= static_cast<long long>(FDA_RANK_MAJOR_ITEMS_PER_CTA) * ctas) return -1;
+  const int n_long = per_group - (short8 * per_group) / 8;
+  return n_long < 1 ? 1 : n_long;
+}
+
 }  // namespace fda

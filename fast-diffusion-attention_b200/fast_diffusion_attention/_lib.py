@@ -50,7 +50,7 @@ class FdaBwdArgs(C.Structure):
 EXPORTS = [
     "fda_fwd_workspace_bytes", "fda_bwd_workspace_bytes", "fda_fwd", "fda_bwd", "fda_bwd_stages", "fda_bwd_noalloc", "fda_strerror",
     "fda_last_cuda_error", "fda_device_status", "fda_version", "fda_geom_key_plan", "fda_geom_query_plan",
-    "fda_geom_classify", "fda_selftest_umma", "fda_selftest_wait",
+    "fda_geom_classify", "fda_geom_item_order", "fda_selftest_umma", "fda_selftest_wait",
 ]
 
 _lib = None
@@ -90,6 +90,8 @@ def load():
         fn.argtypes = [C.c_int] * 6 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int]
     lib.fda_geom_classify.restype = C.c_int
     lib.fda_geom_classify.argtypes = [C.c_int] * 10
+    lib.fda_geom_item_order.restype = C.c_int
+    lib.fda_geom_item_order.argtypes = [C.c_int] * 5 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.fda_selftest_umma.restype = C.c_int
     lib.fda_selftest_umma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     lib.fda_selftest_wait.restype = C.c_int

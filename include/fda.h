@@ -166,6 +166,12 @@ int fda_geom_query_plan(int kh, int k0, int k1, int n, int bs, int bm, int32_t* 
  * mask; bm is unused. */
 int fda_geom_classify(int qh, int kh, int qa, int qb, int k0, int bn, int n, int bs, int bm, int need_full_rows);
 
+/* Position idx of the order in which a persistent kernel takes its items: writes the group (sample x head) and the
+ * rank inside the group (0 = longest item). per_group items per group, n_groups groups, `short8` eighths of a group
+ * counted as short, ctas persistent blocks; returns 0, or -1 for arguments out of range. No counterpart in the
+ * reference (its schedulers are tile_scheduler.hpp:51-482 there). */
+int fda_geom_item_order(int idx, int per_group, int n_groups, int short8, int ctas, int32_t* out_group, int32_t* out_rank);
+
 /* ---- tensor-core self test (GPU): C[128 x n] = A[128 x k] * B with the operand layouts the kernels use ---- */
 /* mode 0: A, B both K-major from shared memory; mode 1: A from tensor memory, B MN-major from shared memory;
  * mode 2: A and B both MN-major from shared memory (the dQ^T product of the single-pass backward).

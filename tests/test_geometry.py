@@ -98,3 +98,34 @@ def test_backward_enumeration(n, bs):
                     covered[(n if qh else 0) + qa:(n if qh else 0) + qb] = True
             want = vis[:, (n if kh else 0) + k0:(n if kh else 0) + k1]
             assert not (want & ~covered).any(), "visible pair not covered"
+
+
+# ------------------------------------------------------------------------------------------------- item order
+@pytest.mark.parametrize("per_group,n_groups,short8,ctas", [
+    (32, 128, 4, 148),    # the benchmark's key tiles on one GPU: 27 items per block, groups one after the other
+    (32, 16, 4, 148),     # an eighth of it: 3.5 items per block, rank for rank over all groups
+    (16, 16, 2, 148),     # its forward items: fewer than two per block
+    (1, 5, 1, 3), (7, 3, 8, 1), (5, 4, 0, 2), (64, 40, 1, 132),
+])
+def test_item_order_visits_every_item_once(per_group, n_groups, short8, ctas):
+    """The order is a permutation of (group, rank); small launches go rank-major (every group's longest items
+    first), large ones group-major with the short ranks of all groups at the end."""
+    lib = _lib.load()
+    g, r = C.c_int32(), C.c_int32()
+    seen = []
+    for idx in range(per_group * n_groups):
+        assert lib.fda_geom_item_order(idx, per_group, n_groups, short8, ctas, C.byref(g), C.byref(r)) == 0
+        assert 0 <= g.value < n_groups and 0 <= r.value < per_group
+        seen.append((g.value, r.value))
+    assert len(set(seen)) == per_group * n_groups
+    total = per_group * n_groups
+    if total <= 8 * ctas:
+        assert seen == [(i % n_groups, i // n_groups) for i in range(total)]
+    else:
+        n_long = max(1, per_group - short8 * per_group // 8)
+        head = seen[: n_long * n_groups]
+        assert head == [(i // n_long, i % n_long) for i in range(n_long * n_groups)]
+        assert all(rank >= n_long for _, rank in seen[n_long * n_groups:])
+    # out of range
+    assert lib.fda_geom_item_order(total, per_group, n_groups, short8, ctas, C.byref(g), C.byref(r)) == -1
+    assert lib.fda_geom_item_order(0, 0, n_groups, short8, ctas, C.byref(g), C.byref(r)) == -1
